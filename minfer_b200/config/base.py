@@ -46,8 +46,8 @@ class LayerSpec:
     block: PartSpec
     mixer: PartSpec
     mixer_norm: PartSpec
-    feed_forward: PartSpec
-    feed_forward_norm: PartSpec
+    feed_forward: Optional[PartSpec]         # None: the layer has no feed-forward (and no norm for it)
+    feed_forward_norm: Optional[PartSpec]
 
 
 @dataclass(frozen=True)

@@ -702,3 +702,184 @@ extern "C" int mf_cast(const void* in, int in_dtype, void* out, int out_dtype, l
         return MF_ERR_UNSUPPORTED;
     return MF_LAUNCH_CHECK();
 }
+
+// ------------------------------------------------------------------------------------
+// a table row added to every row of the float32 residual stream: h[t][:] += table[idx[t]][:]
+// (learned position vectors: idx = the tokens' positions).  An index outside the table sets a
+// status bit and adds nothing.
+// ------------------------------------------------------------------------------------
+template <typename T>
+__global__ void add_rows_kernel(float* __restrict__ h, const T* __restrict__ table,
+                                const int* __restrict__ idx, int width, int n_table,
+                                unsigned* __restrict__ status) {
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    const int r = idx[t];                       // an input of the step
+    pdl_wait();
+    if (r < 0 || r >= n_table) {
+        if (threadIdx.x == 0) atomicOr(status, MF_STATUS_BAD_POSITION);
+        return;
+    }
+    const T* row = table + (size_t)r * width;
+    float* o = h + (size_t)t * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] += to_f32(row[i]);
+}
+
+extern "C" int mf_add_rows(float* h, const void* table, int table_dtype, const int* idx,
+                           int n_rows, int width, int n_table, unsigned* status,
+                           cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    const int threads = width >= 1024 ? 256 : 128;
+    if (table_dtype == MF_DTYPE_F32)
+        mf_launch(add_rows_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, h,
+                  (const float*)table, idx, width, n_table, status);
+    else if (table_dtype == MF_DTYPE_BF16)
+        mf_launch(add_rows_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, h,
+                  (const __nv_bfloat16*)table, idx, width, n_table, status);
+    else
+        return MF_ERR_UNSUPPORTED;
+    return MF_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------------------------
+// RMSNorm followed by a token shift, in float32:
+//     n_t = x_t * rsqrt(mean(x_t^2) + eps) * w        y_t = n_t + (n_{t-1} - n_t) * s
+// n_{t-1} is the normed row of the sequence's position before: the row above in the step, or,
+// for the first token a sequence brings, what the sequence's state holds (zeros at position
+// 0).  The state takes n of the last token a sequence brings.  A row that brings one token
+// reads and writes its state in the same threads; for rows that bring more the state is
+// written by norm_shift_save_kernel, launched behind this one (the block of a row's first
+// token reads the state while the block of its last would write it).
+// ------------------------------------------------------------------------------------
+template <typename TO>
+__global__ void norm_shift_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                  const float* __restrict__ shift,
+                                  const int* __restrict__ positions,
+                                  const int* __restrict__ token_row,
+                                  const int* __restrict__ cu_seqlens,
+                                  const int* __restrict__ slots, float* __restrict__ state,
+                                  TO* __restrict__ y, int width, float eps) {
+    pdl_launch_dependents();
+    __shared__ float scratch[33];
+    const int t = blockIdx.x;
+    const int b = token_row[t];
+    const int pos = positions[t];
+    const bool first = t == cu_seqlens[b];
+    const bool last = t == cu_seqlens[b + 1] - 1;
+    float* st = state + (size_t)slots[b] * width;
+    pdl_wait();
+    const float* xr = x + (size_t)t * width;
+    const float* xp = xr - width;                       // the row above (used unless first)
+    float ss = 0.0f, sp = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = xr[i];
+        ss = fmaf(v, v, ss);
+        if (!first) {
+            const float u = xp[i];
+            sp = fmaf(u, u, sp);
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+    float scale_p = 0.0f;
+    if (!first) {
+        sp = block_sum(sp, scratch);
+        scale_p = 1.0f / sqrtf(sp / (float)width + eps);
+    }
+    TO* yr = y + (size_t)t * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float g = w[i];
+        const float n = xr[i] * scale * g;
+        float before;
+        if (!first) before = xp[i] * scale_p * g;
+        else before = pos > 0 ? st[i] : 0.0f;
+        yr[i] = from_f32<TO>(n + (before - n) * shift[i]);
+        if (first && last) st[i] = n;
+    }
+}
+
+__global__ void norm_shift_save_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                       const int* __restrict__ cu_seqlens,
+                                       const int* __restrict__ slots, float* __restrict__ state,
+                                       int width, float eps) {
+    pdl_launch_dependents();
+    __shared__ float scratch[33];
+    const int b = blockIdx.x;
+    const int lo = cu_seqlens[b], hi = cu_seqlens[b + 1];
+    if (hi - lo < 2) return;                            // nothing, or done by the kernel before
+    float* st = state + (size_t)slots[b] * width;
+    pdl_wait();
+    const float* xr = x + (size_t)(hi - 1) * width;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = xr[i];
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) st[i] = xr[i] * scale * w[i];
+}
+
+// `multi`: some row may bring more than one token (then the second kernel runs too)
+extern "C" int mf_norm_shift(const float* x, const float* w, const float* shift,
+                             const int* positions, const int* token_row, const int* cu_seqlens,
+                             const int* slots, float* state, void* y, int out_dtype, int n_tokens,
+                             int n_rows, int width, float eps, int multi, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    // the block size is a function of the width only, so a row's sum never depends on the batch
+    int threads = 32;
+    while (threads < 512 && threads * 4 < width) threads <<= 1;
+    if (out_dtype == MF_DTYPE_F32)
+        mf_launch(norm_shift_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, x, w, shift,
+                  positions, token_row, cu_seqlens, slots, state, (float*)y, width, eps);
+    else if (out_dtype == MF_DTYPE_BF16)
+        mf_launch(norm_shift_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, x, w,
+                  shift, positions, token_row, cu_seqlens, slots, state, (__nv_bfloat16*)y, width,
+                  eps);
+    else
+        return MF_ERR_UNSUPPORTED;
+    if (multi)
+        mf_launch(norm_shift_save_kernel, dim3(n_rows), dim3(threads), 0, stream, x, w, cu_seqlens,
+                  slots, state, width, eps);
+    return MF_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------------------------
+// xIELU, element by element in float32, with two learned numbers a = (a0, a1):
+//     z > 0:   softplus(a0) z^2 + z/2
+//     z <= 0:  (1/2 + softplus(a1)) (exp(z) - 1 - z) + z/2
+// ------------------------------------------------------------------------------------
+__device__ __forceinline__ float softplus_f32(float x) {
+    return log1pf(expf(-fabsf(x))) + fmaxf(x, 0.0f);
+}
+__device__ __forceinline__ float xielu_f32(float z, float cp, float cn) {
+    return z > 0.0f ? fmaf(cp * z, z, 0.5f * z) : fmaf(cn, expm1f(z) - z, 0.5f * z);
+}
+
+template <typename TI, typename TO>
+__global__ void xielu_kernel(const TI* __restrict__ in, TO* __restrict__ out,
+                             const float* __restrict__ a, long long total) {
+    pdl_launch_dependents();
+    const float cp = softplus_f32(a[0]), cn = 0.5f + softplus_f32(a[1]);      // weights
+    pdl_wait();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x)
+        out[i] = from_f32<TO>(xielu_f32(to_f32(in[i]), cp, cn));
+}
+
+extern "C" int mf_xielu(const void* in, int in_dtype, void* out, int out_dtype, const float* a,
+                        long long total, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    const int threads = 256;
+    const long long cap = (long long)mf_sm_count() * 16;
+    const int blocks = (int)((total + threads - 1) / threads < cap ? (total + threads - 1) / threads : cap);
+#define MF_XIELU(TI, TO) \
+    mf_launch(xielu_kernel<TI, TO>, dim3(blocks), dim3(threads), 0, stream, (const TI*)in, (TO*)out, a, total)
+    if (in_dtype == MF_DTYPE_F32 && out_dtype == MF_DTYPE_F32) MF_XIELU(float, float);
+    else if (in_dtype == MF_DTYPE_F32 && out_dtype == MF_DTYPE_BF16) MF_XIELU(float, __nv_bfloat16);
+    else if (in_dtype == MF_DTYPE_BF16 && out_dtype == MF_DTYPE_BF16)
+        MF_XIELU(__nv_bfloat16, __nv_bfloat16);
+    else return MF_ERR_UNSUPPORTED;
+#undef MF_XIELU
+    return MF_LAUNCH_CHECK();
+}

@@ -116,7 +116,10 @@ class Engine:
         self._call_state: List[Dict[str, torch.Tensor]] = []
         for i, call in enumerate(plan.schedule):
             tensors = {}
-            for req in model.blocks[call.layer].mixer.state_request():
+            block = model.blocks[call.layer]
+            asked = (block.state_request() if hasattr(block, "state_request")
+                     else block.mixer.state_request())
+            for req in asked:
                 tensors[req.name] = self.cache.state.add(f"call{i}.{req.name}", req.shape, req.dtype)
             self._call_state.append(tensors)
         from ..kernels import build

@@ -105,6 +105,11 @@ def _sig_ops(lib: ctypes.CDLL) -> None:
     lib.mf_swiglu.argtypes = [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
     lib.mf_gather_rows.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
     lib.mf_cast.argtypes = [c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p]
+    lib.mf_add_rows.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p,
+                                c_void_p]
+    lib.mf_norm_shift.argtypes = [c_void_p] * 9 + [c_int, c_int, c_int, c_int, c_float, c_int,
+                                                   c_void_p]
+    lib.mf_xielu.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_longlong, c_void_p]
 
 
 def _sig_gemm_simt(lib: ctypes.CDLL) -> None:
@@ -118,6 +123,14 @@ def _sig_attention(lib: ctypes.CDLL) -> None:
     lib.mf_attention_paged.argtypes = ([c_void_p] * 6 + [c_int, c_int, c_void_p, c_void_p] +
                                        [c_int] * 7 + [c_float, c_int, c_int, c_longlong, c_void_p,
                                                       c_int, c_void_p])
+
+
+def _sig_attention_sink(lib: ctypes.CDLL) -> None:
+    lib.mf_unit_norm_kvstore.argtypes = ([c_void_p, c_int] + [c_void_p] * 9 + [c_int] * 7 +
+                                         [c_float, c_int, c_int, c_void_p, c_void_p])
+    lib.mf_sink_attention_packed.argtypes = ([c_void_p] * 9 + [c_int] * 8 + [c_float, c_int, c_void_p])
+    lib.mf_sink_attention_paged.argtypes = ([c_void_p] * 6 + [c_int, c_int] + [c_void_p] * 3 +
+                                            [c_int] * 8 + [c_float, c_int, c_void_p])
 
 
 def _sig_sampling(lib: ctypes.CDLL) -> None:
@@ -160,6 +173,7 @@ def _sig_attention_prefill_tc(lib: ctypes.CDLL) -> None:
 
 
 _SIGNATURES = {"attention_prefill_tc": _sig_attention_prefill_tc,
+               "attention_sink": _sig_attention_sink,
                "attention_prefill": _sig_attention_prefill, "gemm_tc": _sig_gemm_tc, "ops": _sig_ops, "gemm_simt": _sig_gemm_simt, "attention": _sig_attention,
                "sampling": _sig_sampling}
 
@@ -275,6 +289,47 @@ def cast(src: torch.Tensor, out: torch.Tensor) -> None:
         raise KernelError("cast: sizes differ")
     _check(_lib("ops").mf_cast(_ptr(src, "src"), dtype_code(src.dtype), _ptr(out, "out"),
                                dtype_code(out.dtype), src.numel(), _stream()), "cast")
+
+
+def add_rows(h: torch.Tensor, table: torch.Tensor, index: torch.Tensor, status: torch.Tensor) -> None:
+    """h[t] += table[index[t]] in float32 (learned position vectors); an index outside the
+    table sets status bit 2 and adds nothing."""
+    n, width = h.shape
+    if table.dim() != 2 or table.shape[1] != width or index.numel() != n:
+        raise KernelError("add_rows: shapes do not fit")
+    _check(_lib("ops").mf_add_rows(_f32(h, "h"), _ptr(table, "table"), dtype_code(table.dtype),
+                                   _i32(index, "index"), n, width, table.shape[0],
+                                   _i32(status, "status"), _stream()), "add_rows")
+
+
+def norm_shift(x: torch.Tensor, weight: torch.Tensor, shift: torch.Tensor, eps: float,
+               positions: torch.Tensor, token_row: torch.Tensor, cu_seqlens: torch.Tensor,
+               slots: torch.Tensor, state: torch.Tensor, out: torch.Tensor, multi: bool) -> None:
+    """n = rmsnorm(x) * weight; out[t] = n[t] + (n[t-1] - n[t]) * shift, where n[t-1] of the
+    first token a sequence brings is ``state[slot]`` (zeros at position 0); ``state[slot]``
+    takes n of the last token a sequence brings.  ``multi``: some row may bring more than one
+    token."""
+    n, width = out.shape
+    n_rows = slots.numel()
+    if x.shape != (n, width) or weight.numel() != width or shift.numel() != width:
+        raise KernelError("norm_shift: shapes do not fit")
+    if state.dim() != 2 or state.shape[1] != width or cu_seqlens.numel() != n_rows + 1:
+        raise KernelError("norm_shift: the state or the row bounds do not fit")
+    _check(_lib("ops").mf_norm_shift(
+        _f32(x, "x"), _f32(weight, "weight"), _f32(shift, "shift"), _i32(positions, "positions"),
+        _i32(token_row, "token_row"), _i32(cu_seqlens, "cu_seqlens"), _i32(slots, "slots"),
+        _f32(state, "state"), _ptr(out, "out"), dtype_code(out.dtype), n, n_rows, width, float(eps),
+        1 if multi else 0, _stream()), "norm_shift", 2 if multi else 1)
+
+
+def xielu(x: torch.Tensor, params: torch.Tensor, out: torch.Tensor) -> None:
+    """out = softplus(a0) z^2 + z/2 for z > 0, (1/2 + softplus(a1)) (exp(z) - 1 - z) + z/2
+    otherwise; ``params`` = (a0, a1) float32 on the device."""
+    if x.shape != out.shape or params.numel() != 2:
+        raise KernelError("xielu: shapes do not fit")
+    _check(_lib("ops").mf_xielu(_ptr(x, "x"), dtype_code(x.dtype), _ptr(out, "out"),
+                                dtype_code(out.dtype), _f32(params, "params"), x.numel(),
+                                _stream()), "xielu")
 
 
 # ---------------------------------------------------------------------------------------
@@ -621,6 +676,79 @@ def attention_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
 # ---------------------------------------------------------------------------------------
 # sampling
 # ---------------------------------------------------------------------------------------
+# ---------------------------------------------------------------------------------------
+# attention with changed scores and a sink (csrc/attention_sink.cu)
+# ---------------------------------------------------------------------------------------
+def unit_norm_kvstore(qkv: torch.Tensor, positions: torch.Tensor, token_row: torch.Tensor,
+                      seq_end: torch.Tensor, q_out: torch.Tensor, k_out: Optional[torch.Tensor],
+                      v_out: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
+                      v_cache: Optional[torch.Tensor], page_table: Optional[torch.Tensor],
+                      table_stride: int, ring: int, n_heads: int, n_kv: int, head_dim: int,
+                      value_dim: int, eps: float, norm_qk: bool, status: torch.Tensor,
+                      n_partials: int = 0) -> None:
+    """The float32 output of a q|k|v projection (``n_partials`` > 0: its K splits
+    [splits, tokens, width], added here in split order) -> q and k divided by their root mean
+    square per head (``norm_qk``), v unchanged; written as the step's q, k, v and into the
+    cache's pages."""
+    if n_partials > 0:
+        if qkv.dim() != 3 or qkv.shape[0] != n_partials:
+            raise KernelError("unit_norm_kvstore: partial sums must be [splits, tokens, width]")
+        n, width = qkv.shape[1], qkv.shape[2]
+    else:
+        n, width = qkv.shape
+    if width != (n_heads + n_kv) * head_dim + n_kv * value_dim:
+        raise KernelError("unit_norm_kvstore: qkv has the wrong width")
+    dt = q_out.dtype
+    for t in (k_out, v_out, k_cache, v_cache):
+        if t is not None and t.dtype != dt:
+            raise KernelError("unit_norm_kvstore: q, k, v and the cache must share one dtype")
+    if k_cache is not None and (k_cache.shape[-1] != head_dim or v_cache.shape[-1] != value_dim):
+        raise KernelError("unit_norm_kvstore: the cache has other key or value widths")
+    _check(_lib("attention_sink").mf_unit_norm_kvstore(
+        _f32(qkv, "qkv"), int(n_partials), _i32(positions, "positions"),
+        _i32(token_row, "token_row"), _i32(seq_end, "seq_end"), _ptr(q_out, "q_out"),
+        _ptr(k_out, "k_out"), _ptr(v_out, "v_out"), _ptr(k_cache, "k_cache"),
+        _ptr(v_cache, "v_cache"), _i32(page_table, "page_table"), int(table_stride), int(ring),
+        n, n_heads, n_kv, head_dim, value_dim, float(eps), 1 if norm_qk else 0, dtype_code(dt),
+        _i32(status, "status"), _stream()), "unit_norm_kvstore")
+
+
+def sink_attention_packed(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, row_seq: torch.Tensor,
+                          row_pos: torch.Tensor, cu_seqlens: torch.Tensor, out: torch.Tensor,
+                          r1: Optional[torch.Tensor], r2: Optional[torch.Tensor], n_heads: int,
+                          n_kv: int, head_dim: int, value_dim: int, window: int, chunk: int,
+                          sink: bool, scale: float) -> None:
+    """Attention of the step's own packed keys and values (whole prompts): scores
+    (q . k) * scale - r1 ln(1 + r2 (i - j)), causal, optional window and chunk mask, a sink
+    of score 0 in the softmax if ``sink``."""
+    rows = q.shape[0]
+    if out.shape != (rows, n_heads * value_dim) or (r1 is None) != (r2 is None):
+        raise KernelError("sink_attention_packed: shapes do not fit")
+    _check(_lib("attention_sink").mf_sink_attention_packed(
+        _ptr(q, "q"), _ptr(k, "k"), _ptr(v, "v"), _i32(row_seq, "row_seq"), _i32(row_pos, "row_pos"),
+        _i32(cu_seqlens, "cu_seqlens"), _ptr(out, "out"), _f32(r1, "r1"), _f32(r2, "r2"), rows,
+        n_heads, n_kv, head_dim, value_dim, int(window), int(chunk), 1 if sink else 0, float(scale),
+        dtype_code(q.dtype), _stream()), "sink_attention_packed")
+
+
+def sink_attention_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                         row_seq: torch.Tensor, row_pos: torch.Tensor, page_table: torch.Tensor,
+                         table_stride: int, ring: int, out: torch.Tensor,
+                         r1: Optional[torch.Tensor], r2: Optional[torch.Tensor], n_heads: int,
+                         n_kv: int, head_dim: int, value_dim: int, window: int, chunk: int,
+                         sink: bool, scale: float) -> None:
+    """The same over the paged cache: every row of ``q`` is a query at its own position."""
+    rows = q.shape[0]
+    if out.shape != (rows, n_heads * value_dim) or (r1 is None) != (r2 is None):
+        raise KernelError("sink_attention_paged: shapes do not fit")
+    _check(_lib("attention_sink").mf_sink_attention_paged(
+        _ptr(q, "q"), _ptr(k_cache, "k_cache"), _ptr(v_cache, "v_cache"), _i32(row_seq, "row_seq"),
+        _i32(row_pos, "row_pos"), _i32(page_table, "page_table"), int(table_stride), int(ring),
+        _ptr(out, "out"), _f32(r1, "r1"), _f32(r2, "r2"), rows, n_heads, n_kv, head_dim, value_dim,
+        int(window), int(chunk), 1 if sink else 0, float(scale), dtype_code(q.dtype), _stream()),
+        "sink_attention_paged")
+
+
 def sampler_state_ints() -> int:
     return int(_lib("sampling").mf_sampler_state_ints())
 

@@ -36,6 +36,7 @@ LIBRARIES = {
     "gemm_tc": ("gemm_tc.cu", []),
     "attention_prefill": ("attention_prefill.cu", []),
     "attention_prefill_tc": ("attention_prefill_tc.cu", []),
+    "attention_sink": ("attention_sink.cu", []),
 }
 
 

@@ -5,13 +5,20 @@ from .base import (Block, CacheRequest, CacheView, CallBinding, FeedForward, Mix
                    PositionEncoding, StateRequest, StepContext)
 from .block import PreNormBlock
 from .linear import Linear
-from .mlp import GatedMlp
+from .mlp import DenseMlp, GatedMlp
 from .norm import RmsNorm
+from .positions import LearnedPositions
 from .rotary import NoPosition, Rotary
+from .shift import TokenShift
+from .sink_attention import SinkAttention
 
 register_part("norm", "rms_norm", RmsNorm, replace=True)
 register_part("position", "rotary", Rotary, replace=True)
 register_part("position", "none", NoPosition, replace=True)
 register_part("mixer", "attention", Attention, replace=True)
+register_part("mixer", "sink_attention", SinkAttention, replace=True)
 register_part("feed_forward", "gated_mlp", GatedMlp, replace=True)
-register_part("block", "pre_norm", lambda layer: PreNormBlock(layer), replace=True)
+register_part("feed_forward", "dense_mlp", DenseMlp, replace=True)
+register_part("model", "learned_positions", LearnedPositions, replace=True)
+register_part("block", "pre_norm", lambda layer, **options: PreNormBlock(layer, **options),
+              replace=True)

@@ -237,6 +237,11 @@ class Block(Part):
         norm's input prepared by the product before it (``Prepared``); else None."""
         return None
 
+    def state_request(self) -> Sequence[StateRequest]:
+        """Fixed-size state per sequence that a call of this block keeps: the mixer's, plus
+        whatever the block keeps itself."""
+        return tuple(self.mixer.state_request())
+
     def parts(self) -> Sequence[Part]:
         """Every part this block runs, whatever it calls them; the engine asks each whether it
         can be captured into a CUDA graph and which kernel libraries it needs."""

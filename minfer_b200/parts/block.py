@@ -1,28 +1,44 @@
 """Pre-norm block with two residual adds: h += mixer(norm1(h)); h += ffn(norm2(h))
-(src/models/qwen2/graph.rs:59-64, 137, 154-155, 176)."""
+(src/models/qwen2/graph.rs:59-64, 137, 154-155, 176).
+
+Two options: a layer without a feed-forward (``LayerSpec.feed_forward`` None: the second half
+is left out, norm and all), and a token shift between the first norm and the mixer
+(``token_shift``: the parameters of ``parts.shift.TokenShift``), whose per-sequence state the
+block asks the cache for beside the mixer's own."""
 from __future__ import annotations
 
-from typing import Dict, List
+from typing import Any, Dict, List, Mapping, Optional, Sequence
 
 import torch
 
 from ..config.base import LayerSpec
-from .base import Block, CallBinding, StepContext
+from .base import Block, CallBinding, StateRequest, StepContext, settle_pending
 
 
 class PreNormBlock(Block):
     capturable = True      # launches kernels only; safe inside a CUDA graph capture
 
-    def __init__(self, layer: LayerSpec):
+    def __init__(self, layer: LayerSpec, token_shift: Optional[Mapping[str, Any]] = None):
         from ..registry import build_part
         self.prefix = layer.prefix
         self.mixer_norm = build_part("norm", layer.mixer_norm)
         self.mixer = build_part("mixer", layer.mixer)
-        self.feed_forward_norm = build_part("norm", layer.feed_forward_norm)
-        self.feed_forward = build_part("feed_forward", layer.feed_forward)
+        self.feed_forward_norm = self.feed_forward = None
+        if layer.feed_forward is not None:
+            self.feed_forward_norm = build_part("norm", layer.feed_forward_norm)
+            self.feed_forward = build_part("feed_forward", layer.feed_forward)
+        self.shift = None
+        if token_shift is not None:
+            from .shift import TokenShift
+            self.shift = TokenShift(**token_shift)
 
     def parts(self):
-        return (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward)
+        return tuple(p for p in (self.mixer_norm, self.shift, self.mixer, self.feed_forward_norm,
+                                 self.feed_forward) if p is not None)
+
+    def state_request(self) -> Sequence[StateRequest]:
+        own = tuple(self.shift.state_request()) if self.shift is not None else ()
+        return tuple(self.mixer.state_request()) + own
 
     def tensor_specs(self, prefix: str = "") -> List:
         specs = []
@@ -43,6 +59,8 @@ class PreNormBlock(Block):
     accepts_pending = True     # its norms add a pending projection output while reading h
 
     def entry_norm(self):
+        if self.shift is not None:
+            return None            # the shift mixes normed rows: the norm cannot ride on a product
         if self.mixer_norm.foldable() is not None and getattr(self.mixer, "accepts_row_scale", False):
             return self.mixer_norm
         return None
@@ -72,16 +90,24 @@ class PreNormBlock(Block):
             ctx.extras.pop("prepare_for", None)
 
     def mix(self, h: torch.Tensor, ctx: StepContext, binding: CallBinding) -> None:
-        x, scale = self._normed(self.mixer_norm, h, ctx, self.mixer)
+        if self.shift is not None:
+            ctx.extras.pop("prepared", None)
+            settle_pending(ctx, h)
+            x, scale = self.shift.norm_and_shift(self.mixer_norm, h, ctx, binding.state), None
+        else:
+            x, scale = self._normed(self.mixer_norm, h, ctx, self.mixer)
         # the mixer's last product may prepare the input of the norm before the feed-forward,
         # unless the engine drops rows of h between the two
         target = None
-        if (ctx.extras.get("rows_stay", True) and self.feed_forward_norm.foldable() is not None
+        if (self.feed_forward is not None and ctx.extras.get("rows_stay", True)
+                and self.feed_forward_norm.foldable() is not None
                 and getattr(self.feed_forward, "accepts_row_scale", False)):
             target = self.feed_forward_norm
         self._call(self.mixer, x, scale, ctx, target, binding, h)
 
     def feed(self, h: torch.Tensor, ctx: StepContext) -> None:
+        if self.feed_forward is None:
+            return
         x, scale = self._normed(self.feed_forward_norm, h, ctx, self.feed_forward)
         # the feed-forward's last product may prepare the input of the norm that reads h next
         # (the next block's first, or the model's last), which the engine names

@@ -13,7 +13,7 @@ from typing import Dict, List, Optional
 import torch
 
 from ..kernels import api as K
-from ..weights.spec import MATRIX, Init, TensorSpec
+from ..weights.spec import MATRIX, VECTOR, Init, TensorSpec
 from .base import FeedForward, StepContext, settle_pending
 from .linear import Linear
 
@@ -90,6 +90,74 @@ class GatedMlp(FeedForward):
                 raise K.KernelError("a row scale needs the tensor-core product")
             gu = self.gate_up.forward(x, ctx.act_dtype)
             K.swiglu(gu, act, self.interleaved)
+        target = ctx.extras.pop("prepare_for", None)
+        if target is not None:
+            settle_pending(ctx, residual)
+            prepared = self.down.accumulate_prepared(act, residual, target)
+            if prepared is not None:
+                ctx.extras["prepared"] = prepared
+                return
+        pending = self.down.partial_sums(act)
+        if pending is None:
+            self.down.forward(act, torch.float32, out=residual, accumulate=True)
+        else:
+            settle_pending(ctx, residual)          # never two at once
+            ctx.extras["pending"] = pending
+
+
+class DenseMlp(FeedForward):
+    """Feed-forward without a gate: down( act(up(x)) ), no biases.  ``activation``:
+
+    ``"xielu"``  with two learned numbers a = (a0, a1) in the tensor ``act_name``:
+                 z > 0: softplus(a0) z^2 + z/2;  z <= 0: (1/2 + softplus(a1)) (exp(z) - 1 - z) + z/2,
+                 evaluated in float32 on the product's float32 sums.
+
+    Tensor names are parameters (``up_name``, ``down_name``, ``act_name``, each behind the
+    layer's prefix)."""
+
+    capturable = True      # launches kernels only; safe inside a CUDA graph capture
+    ACTIVATIONS = ("xielu",)
+
+    def libraries(self, dtype: torch.dtype) -> List[str]:
+        return ["ops", "gemm_tc"] if dtype == torch.bfloat16 else ["ops", "gemm_simt"]
+
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "xielu",
+                 up_name: str = "mlp.up", down_name: str = "mlp.down", act_name: str = "mlp.act",
+                 init_std: float = 0.02):
+        if activation not in self.ACTIVATIONS:
+            raise ValueError(f"the dense feed-forward has the activations {self.ACTIVATIONS}, got "
+                             f"{activation!r}")
+        self.hidden_size = int(hidden_size)
+        self.intermediate_size = int(intermediate_size)
+        self.activation = activation
+        self.up_name, self.down_name, self.act_name = up_name, down_name, act_name
+        self.init_std = float(init_std)
+        self.up: Optional[Linear] = None
+        self.down: Optional[Linear] = None
+        self.act_params: Optional[torch.Tensor] = None
+
+    def tensor_specs(self, prefix: str) -> List[TensorSpec]:
+        init = Init(0.0, self.init_std)
+        return [TensorSpec(f"{prefix}{self.up_name}", (self.intermediate_size, self.hidden_size),
+                           MATRIX, init),
+                TensorSpec(f"{prefix}{self.down_name}", (self.hidden_size, self.intermediate_size),
+                           MATRIX, init),
+                TensorSpec(f"{prefix}{self.act_name}", (2,), VECTOR, Init(0.0, 0.5))]
+
+    def load(self, prefix: str, weights: Dict[str, torch.Tensor]) -> None:
+        self.up = Linear(weights[f"{prefix}{self.up_name}"])
+        self.down = Linear(weights[f"{prefix}{self.down_name}"])
+        self.act_params = weights[f"{prefix}{self.act_name}"]
+        self.accepts_row_scale = self.up.takes_row_scale()
+
+    def export(self, prefix: str) -> Dict[str, torch.Tensor]:
+        return {f"{prefix}{self.up_name}": self.up.weight, f"{prefix}{self.down_name}": self.down.weight,
+                f"{prefix}{self.act_name}": self.act_params}
+
+    def forward_add(self, x: torch.Tensor, ctx: StepContext, residual: torch.Tensor) -> None:
+        act = torch.empty((x.shape[0], self.intermediate_size), dtype=ctx.act_dtype, device=x.device)
+        z = self.up.forward(x, torch.float32, row_scale=ctx.input_scale)
+        K.xielu(z, self.act_params, act)
         target = ctx.extras.pop("prepare_for", None)
         if target is not None:
             settle_pending(ctx, residual)

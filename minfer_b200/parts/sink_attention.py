@@ -1,0 +1,183 @@
+"""Attention whose scores are changed before the softmax, with a sink, as a mixer.
+
+    q, k, v = Wq u, Wk u, Wv u (no biases; v of its own width ``value_dim``)
+    q, k divided by their root mean square per head, no weight           (``qk_norm``)
+    s_ij = (q_i . k_j) * scale - r1_h ln(1 + r2_h (i - j))               (``distance_bias``)
+    j visible from i iff j <= i, floor(i / chunk) == floor(j / chunk)    (``chunk`` > 0, counted
+    from position 0 of the sequence), i - j < window                      (``window`` > 0)
+    w_ij = exp(s_ij) / (1 + sum_j' exp(s_ij'))                           (``sink``)
+    out = Wo concat_h(sum_j w_ij v_j)
+
+Every size, constant and switch is a parameter; the tensors' names are too (behind
+``prefix + tensor_prefix``).  One packed product gives q|k|v in float32; one kernel norms q and
+k and writes the step's keys and values and the cache's pages; attention runs over the step's
+own keys for whole prompts and over the cache otherwise; Wo adds into the residual stream.
+
+A query never looks further back than its chunk's start (or its window), so the cache keeps a
+ring of that many positions plus what a step may add, as for a windowed layer.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ..kernels import api as K
+from ..weights.spec import MATRIX, VECTOR, Init, TensorSpec
+from .base import CacheRequest, CallBinding, Mixer, StepContext, settle_pending
+from .linear import Linear
+
+
+class SinkAttention(Mixer):
+    capturable = True      # launches kernels only; safe inside a CUDA graph capture
+
+    def libraries(self, dtype: torch.dtype) -> List[str]:
+        libs = ["ops", "attention_sink"]
+        libs.append("gemm_tc" if dtype == torch.bfloat16 else "gemm_simt")
+        return libs
+
+    def __init__(self, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int,
+                 value_dim: int, scale: float, norm_eps: float, chunk: int = 0, window: int = 0,
+                 sink: bool = True, qk_norm: bool = True, distance_bias: bool = True,
+                 tensor_prefix: str = "mix.", init_std: float = 0.02):
+        if n_kv_heads < 1 or n_heads % n_kv_heads != 0:
+            raise ValueError(f"{n_heads} heads do not divide into {n_kv_heads} key/value heads")
+        for what, d in (("key", head_dim), ("value", value_dim)):
+            if not 1 <= d <= 256:
+                raise ValueError(f"{what} size {d} is not supported: the kernels take 1 to 256")
+        if chunk < 0 or window < 0:
+            raise ValueError("chunk and window must not be negative")
+        self.hidden_size = int(hidden_size)
+        self.n_heads = int(n_heads)
+        self.n_kv_heads = int(n_kv_heads)
+        self.head_dim = int(head_dim)
+        self.value_dim = int(value_dim)
+        self.scale = float(scale)
+        self.norm_eps = float(norm_eps)
+        self.chunk = int(chunk)
+        self.window = int(window)
+        self.sink = bool(sink)
+        self.qk_norm = bool(qk_norm)
+        self.distance_bias = bool(distance_bias)
+        self.tensor_prefix = tensor_prefix
+        self.init_std = float(init_std)
+        self.qkv: Optional[Linear] = None
+        self.out: Optional[Linear] = None
+        self.r1: Optional[torch.Tensor] = None
+        self.r2: Optional[torch.Tensor] = None
+
+    # ---- how far back a query may look ----------------------------------------------------
+    def reach(self) -> int:
+        """Positions a query may look back, itself included (0: no bound)."""
+        bounds = [b for b in (self.chunk, self.window) if b > 0]
+        return min(bounds) if bounds else 0
+
+    # ---- weights ----------------------------------------------------------------------
+    def tensor_specs(self, prefix: str) -> List[TensorSpec]:
+        p = f"{prefix}{self.tensor_prefix}"
+        nq, nk, nv = (self.n_heads * self.head_dim, self.n_kv_heads * self.head_dim,
+                      self.n_kv_heads * self.value_dim)
+        init = Init(0.0, self.init_std)
+        specs = [TensorSpec(f"{p}q", (nq, self.hidden_size), MATRIX, init),
+                 TensorSpec(f"{p}k", (nk, self.hidden_size), MATRIX, init),
+                 TensorSpec(f"{p}v", (nv, self.hidden_size), MATRIX, init),
+                 TensorSpec(f"{p}o", (self.hidden_size, self.n_heads * self.value_dim), MATRIX, init)]
+        if self.distance_bias:
+            specs += [TensorSpec(f"{p}r1", (self.n_heads,), VECTOR, Init(0.5, 0.1)),
+                      TensorSpec(f"{p}r2", (self.n_heads,), VECTOR, Init(0.5, 0.1))]
+        return specs
+
+    def load(self, prefix: str, weights: Dict[str, torch.Tensor]) -> None:
+        p = f"{prefix}{self.tensor_prefix}"
+        parts = [weights[f"{p}{n}"] for n in "qkv"]
+        if len({t.dtype for t in parts}) != 1:
+            parts = [t.to(torch.float32) for t in parts]
+        self.qkv = Linear(torch.cat(parts, dim=0).contiguous())
+        self.out = Linear(weights[f"{p}o"])
+        if self.distance_bias:
+            self.r1, self.r2 = weights[f"{p}r1"], weights[f"{p}r2"]
+        # the projection of q|k|v can apply a norm's 1/rms itself (bfloat16 on tensor cores)
+        self.accepts_row_scale = self.qkv.takes_row_scale()
+
+    def export(self, prefix: str) -> Dict[str, torch.Tensor]:
+        p = f"{prefix}{self.tensor_prefix}"
+        nq, nk = self.n_heads * self.head_dim, self.n_kv_heads * self.head_dim
+        nv = self.n_kv_heads * self.value_dim
+        out = {f"{p}q": self.qkv.weight[:nq], f"{p}k": self.qkv.weight[nq:nq + nk],
+               f"{p}v": self.qkv.weight[nq + nk:nq + nk + nv], f"{p}o": self.out.weight}
+        if self.distance_bias:
+            out[f"{p}r1"], out[f"{p}r2"] = self.r1, self.r2
+        return out
+
+    # ---- what it keeps per sequence -----------------------------------------------------
+    def cache_request(self) -> Optional[CacheRequest]:
+        return CacheRequest(self.n_kv_heads, self.head_dim, self.reach(),
+                            self.value_dim if self.value_dim != self.head_dim else 0)
+
+    # ---- the step -----------------------------------------------------------------------
+    def forward_add(self, x: torch.Tensor, ctx: StepContext, binding: CallBinding,
+                    residual: torch.Tensor) -> None:
+        n = x.shape[0]
+        nh, nk, hd, vd = self.n_heads, self.n_kv_heads, self.head_dim, self.value_dim
+        dev, act = x.device, ctx.act_dtype
+        cache = binding.cache
+        if cache is None:
+            raise K.KernelError("the attention mixer was given no cache entry")
+        if cache.k.dtype != act:
+            raise K.KernelError("the cache and the activations must share one dtype")
+        # the K splits of a small projection are added by the kernel that norms q and k
+        split = self.qkv.partial_sums(x, row_scale=ctx.input_scale)
+        if split is not None:
+            qkv, n_partials = split.partial, split.partial.shape[0]
+        else:
+            qkv, n_partials = self.qkv.forward(x, torch.float32, row_scale=ctx.input_scale), 0
+        q = torch.empty((n, nh, hd), dtype=act, device=dev)
+        write = binding.writes_cache
+        own_kv = ctx.from_start
+        k_step = v_step = None
+        if own_kv and write:
+            k_step = torch.empty((n, nk, hd), dtype=act, device=dev)
+            v_step = torch.empty((n, nk, vd), dtype=act, device=dev)
+            if binding.has_readers:
+                ctx.extras[("step_kv", binding.entry)] = (k_step, v_step)
+        elif own_kv:
+            k_step, v_step = ctx.extras[("step_kv", binding.entry)]
+        K.unit_norm_kvstore(qkv, ctx.positions, ctx.token_row, ctx.seq_end, q,
+                            k_step if write else None, v_step if write else None,
+                            cache.k if write else None, cache.v if write else None,
+                            cache.page_table if write else None, cache.table_stride, cache.ring,
+                            nh, nk, hd, vd, self.norm_eps, self.qk_norm, ctx.status,
+                            n_partials=n_partials)
+        o = torch.empty((n, nh * vd), dtype=act, device=dev)
+        if own_kv:
+            K.sink_attention_packed(q, k_step, v_step, ctx.token_row, ctx.positions,
+                                    ctx.cu_seqlens, o, self.r1, self.r2, nh, nk, hd, vd,
+                                    self.window, self.chunk, self.sink, self.scale)
+        else:
+            reach = self.reach()
+            if cache.ring and ctx.max_row_tokens > cache.ring - reach + 1:
+                raise K.KernelError(
+                    f"a sequence brings {ctx.max_row_tokens} tokens, but a ring of {cache.ring} "
+                    f"positions with a reach of {reach} takes {cache.ring - reach + 1} a step "
+                    f"(the engine runs longer rows in portions)")
+            K.sink_attention_paged(q, cache.k, cache.v, ctx.token_row, ctx.positions,
+                                   cache.page_table, cache.table_stride, cache.ring, o, self.r1,
+                                   self.r2, nh, nk, hd, vd, self.window, self.chunk, self.sink,
+                                   self.scale)
+        self._project_out(o, ctx, residual)
+
+    def _project_out(self, o: torch.Tensor, ctx: StepContext, residual: torch.Tensor) -> None:
+        target = ctx.extras.pop("prepare_for", None)
+        if target is not None:
+            # the product completes the residual and prepares the next norm's input
+            settle_pending(ctx, residual)
+            prepared = self.out.accumulate_prepared(o, residual, target)
+            if prepared is not None:
+                ctx.extras["prepared"] = prepared
+                return
+        pending = self.out.partial_sums(o)
+        if pending is None:
+            self.out.forward(o, torch.float32, out=residual, accumulate=True)
+        else:
+            settle_pending(ctx, residual)          # never two at once
+            ctx.extras["pending"] = pending

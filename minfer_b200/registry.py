@@ -46,7 +46,11 @@ def known_architectures() -> list[str]:
 
 
 def architecture_name(config: Mapping[str, Any], where: str = "config.json") -> str:
+    """The model class a config.json names: the first entry of its list ``architectures``,
+    or, in configurations that name just one, the string ``architecture``."""
     archs = config.get("architectures")
+    if archs is None and isinstance(config.get("architecture"), str):
+        return config["architecture"]
     if not isinstance(archs, (list, tuple)) or not archs or not isinstance(archs[0], str):
         raise ConfigError(f"{where}: key 'architectures' must be a non-empty list of names")
     return archs[0]

@@ -40,7 +40,10 @@ def main(argv=None) -> int:
         return 2
     os.makedirs(args.out, exist_ok=True)
     model = Model.from_folder(args.model, args.dtype, "cuda:0")
-    engine = Engine(model, max_tokens=args.max_tokens)
+    # the cache hands out pages of 64 positions: a request may hold up to 63 positions more
+    # than its tokens, so the pool gets a page per slot on top of what the caller counted
+    max_seqs = 256
+    engine = Engine(model, max_tokens=args.max_tokens + 64 * max_seqs, max_seqs=max_seqs)
     slot_of: Dict[str, int] = {}
 
     for line in sys.stdin:

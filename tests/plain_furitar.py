@@ -145,3 +145,26 @@ def forward(config: dict, w: Dict[str, torch.Tensor], tokens: List[int],
     st.length += len(tokens)
     logits = (rms_norm(x, w["final.norm"], eps) @ w["head"].T) * float(config["logit_scale"])
     return logits, st
+
+
+def load_folder(folder: str, dtype: torch.dtype = torch.float64):
+    import json
+    import os
+    from safetensors import safe_open
+    with open(os.path.join(folder, "config.json")) as f:
+        cfg = json.load(f)
+    weights = {}
+    with safe_open(os.path.join(folder, "model.safetensors"), framework="pt") as f:
+        for name in f.keys():
+            weights[name] = f.get_tensor(name).to(dtype)
+    return cfg, weights
+
+
+def generate_greedy(config: dict, w: Dict[str, torch.Tensor], prompt: List[int], n_new: int) -> List[int]:
+    logits, st = forward(config, w, list(prompt))
+    out = []
+    for _ in range(n_new):
+        tok = int(torch.argmax(logits[-1]))
+        out.append(tok)
+        logits, st = forward(config, w, [tok], st)
+    return out

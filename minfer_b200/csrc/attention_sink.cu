@@ -19,7 +19,9 @@
 //     as the step's packed q, k, v and into the paged cache.
 //   * sink_attention_generic: any sizes, float32 or bfloat16, keys from the step's packed
 //     rows (whole prompts) or from the paged cache; one warp per (query, head).
-//   * sink_attention_group (further down): bfloat16 on tensor cores.
+//   * sink_attention_mma (further down): prompts and their portions, bfloat16 on tensor cores.
+//   * sink_attention_decode (further down): single tokens over the cache, bfloat16 on tensor
+//     cores, the query heads of a key/value head as the rows of the product.
 #include "common.cuh"
 
 #define SA_WARPS 4
@@ -347,4 +349,357 @@ extern "C" int mf_sink_attention_paged(const void* q, const void* k_cache, const
     if (bad) return bad;
     if (page_table == nullptr) return MF_ERR_ARGUMENT;
     return sink_generic_launch<true>(a, dtype, stream);
+}
+
+// ------------------------------------------------------------------------------------------
+// Prompts and portions of prompts on tensor cores (bfloat16; key and value sizes multiples of
+// 8 up to 128, padded with zeros in shared memory to 64 or 128).
+//
+// A CTA owns 64 queries of one head of one sequence and walks the keys its queries can see in
+// tiles of 64 absolute positions (a page of the cache, or 64 packed rows) with an online
+// softmax in base 2: S = Q K^T and O += P V are m16n8k16 bf16 MMAs with float32
+// accumulation; K and V tiles are double-buffered in shared memory by cp.async with an XOR
+// swizzle; fragments come out by ldmatrix (transposed for V).  The queries are the step's
+// packed rows; row i of a sequence is at position start + i, start = seq_end - rows (0 for
+// whole prompts).  The distance bias in base-2 units, r1 log2(1 + r2 d), comes from a table in
+// shared memory when the reach is bounded (a chunk or a window of up to 4,096), else it is
+// computed per score.  The sink enters at the end: l += 2^(-m) with m >= 0 from the start.
+// ------------------------------------------------------------------------------------------
+#define SM_WARPS 4
+#define SM_ROWS 64
+#define SM_KEYS 64
+#define SM_MAX_TAB 4096
+
+struct SinkMmaArgs {
+    const __nv_bfloat16* q;   // [tokens][n_heads][hd]
+    const __nv_bfloat16* k;   // packed [tokens][n_kv][hd], or the cache [pages][n_kv][64][hd]
+    const __nv_bfloat16* v;   // packed [tokens][n_kv][vd], or the cache [pages][n_kv][64][vd]
+    const int* cu_seqlens;    // [rows + 1] tokens each sequence brings in this step
+    const int* seq_end;       // [rows] length after the step (paged source; null: start at 0)
+    const int* page_table;
+    int table_stride, ring;
+    __nv_bfloat16* out;       // [tokens][n_heads * vd]
+    const float* r1;          // [n_heads] or null
+    const float* r2;
+    int n_heads, n_kv, hd, vd, window, chunk, sink;
+    int tab_n;                // entries of the bias table (0: the bias is computed per score)
+    float scale_log2;         // scale * log2(e)
+};
+
+__device__ __forceinline__ void sm_mma16816(float* d, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t sm_pack2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ void sm_ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                           uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void sm_ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1,
+                                                 uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+
+// Copies `n_rows` rows (ROWS at most) of `d` elements each, `row_stride` elements apart, into a
+// swizzled [ROWS][DP] tile; rows at or beyond `n_valid` and the columns from `d` to DP are
+// filled with zeros.  A thread always copies the same 16-byte column.
+template <int DP, int ROWS, int THREADS>
+struct SinkTileCopy {
+    static constexpr int CPR = DP / 8;                    // 16-byte chunks per padded row
+    static constexpr int RPP = THREADS / CPR;             // rows per pass
+    int r0;
+    uint32_t dst_off;
+    int src_col;
+    bool col_ok;
+    __device__ __forceinline__ SinkTileCopy(int tid, int d) {
+        r0 = tid / CPR;
+        const int c = tid % CPR;
+        dst_off = (uint32_t)((r0 * CPR + (c ^ (r0 & 7))) * 16);
+        src_col = c * 8;
+        col_ok = src_col < d;
+    }
+    __device__ __forceinline__ void load(uint32_t tile, const __nv_bfloat16* base,
+                                         long long row_stride, int n_valid) const {
+        const __nv_bfloat16* src = base + (long long)r0 * row_stride + src_col;
+#pragma unroll
+        for (int j = 0; j < ROWS / RPP; ++j) {
+            const bool ok = col_ok && r0 + j * RPP < n_valid;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+                         ::"r"(tile + dst_off + (uint32_t)(j * RPP * CPR * 16)),
+                           "l"(ok ? src + (long long)j * RPP * row_stride : base), "r"(ok ? 16 : 0)
+                         : "memory");
+        }
+    }
+};
+
+template <int HDP, int VDP, bool PAGED>
+__global__ void __launch_bounds__(SM_WARPS * 32, (HDP + VDP > 128) ? 2 : 3)
+sink_attention_mma_kernel(SinkMmaArgs a) {
+    pdl_launch_dependents();
+    constexpr int CPRK = HDP / 8, CPRV = VDP / 8;
+    extern __shared__ __align__(128) uint8_t sm_smem[];
+    const uint32_t k_s = (uint32_t)__cvta_generic_to_shared(sm_smem);           // [2][64][HDP]
+    const uint32_t v_s = k_s + 2 * 64 * HDP * 2;                                 // [2][64][VDP]
+    float* tab = (float*)(sm_smem + 2 * 64 * (HDP + VDP) * 2);                   // [tab_n]
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int seq = blockIdx.z, head = blockIdx.y;
+    const int tok0 = a.cu_seqlens[seq];
+    const int n_new = a.cu_seqlens[seq + 1] - tok0;
+    // heavy (late) query tiles first: they have the most keys
+    const int q_tile = (int)gridDim.x - 1 - (int)blockIdx.x;
+    const int q0 = q_tile * SM_ROWS;
+    if (q0 >= n_new) return;
+    const int end = a.seq_end != nullptr ? a.seq_end[seq] : n_new;
+    const int start = end - n_new;
+    const int hk = head / (a.n_heads / a.n_kv);
+    const int hd = a.hd, vd = a.vd;
+    const bool has_bias = a.r1 != nullptr;
+    const float r1 = has_bias ? a.r1[head] : 0.0f, r2 = has_bias ? a.r2[head] : 0.0f;
+    // the bias table of this head (weights: before the wait)
+    for (int d = tid; d < a.tab_n; d += SM_WARPS * 32) tab[d] = r1 * log2f(fmaf(r2, (float)d, 1.0f));
+    pdl_wait();
+
+    const int pos0 = start + q0;                                   // position of the tile's first query
+    const int pos_last = start + min(q0 + SM_ROWS, n_new) - 1;
+    const int kt_begin = sink_first_key(pos0, a.window, a.chunk) / SM_KEYS;
+    const int kt_end = pos_last / SM_KEYS;                         // inclusive
+
+    const SinkTileCopy<HDP, 64, SM_WARPS * 32> copy_k(tid, hd);
+    const SinkTileCopy<VDP, 64, SM_WARPS * 32> copy_v(tid, vd);
+    auto load_tile = [&](int kt, int buf) {
+        const int key0 = kt * SM_KEYS;
+        const __nv_bfloat16 *kb, *vb;
+        long long ks, vs;
+        if (PAGED) {
+            const int p_eff = a.ring > 0 ? key0 % a.ring : key0;
+            int page = a.page_table[(size_t)seq * a.table_stride + (p_eff >> 6)];
+            if (page < 0) page = 0;                                // (masked anyway: beyond the end)
+            kb = a.k + ((long long)page * a.n_kv + hk) * MF_PAGE * hd;
+            vb = a.v + ((long long)page * a.n_kv + hk) * MF_PAGE * vd;
+            ks = hd; vs = vd;
+        } else {
+            kb = a.k + ((long long)(tok0 + key0) * a.n_kv + hk) * hd;
+            vb = a.v + ((long long)(tok0 + key0) * a.n_kv + hk) * vd;
+            ks = (long long)a.n_kv * hd; vs = (long long)a.n_kv * vd;
+        }
+        copy_k.load(k_s + (uint32_t)(buf * 64 * HDP * 2), kb, ks, end - key0);
+        copy_v.load(v_s + (uint32_t)(buf * 64 * VDP * 2), vb, vs, end - key0);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    load_tile(kt_begin, 0);
+
+    // the sink starts the running maximum at its score, 0
+    float m_r[2], l_r[2] = {0.0f, 0.0f};
+    m_r[0] = m_r[1] = a.sink ? 0.0f : -INFINITY;
+    float o[VDP / 8][4];
+#pragma unroll
+    for (int i = 0; i < VDP / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
+    const int qi = q0 + warp * 16 + g;                            // this thread's queries: qi, qi + 8
+    int row_p[2], row_lo[2];
+    row_p[0] = start + qi; row_p[1] = row_p[0] + 8;
+    row_lo[0] = sink_first_key(row_p[0], a.window, a.chunk);
+    row_lo[1] = sink_first_key(row_p[1], a.window, a.chunk);
+    const int warp_lo_max = sink_first_key(pos0 + warp * 16 + 15, a.window, a.chunk);
+    // query fragments straight from global memory (rows beyond the end and columns beyond hd: 0)
+    uint32_t qa[HDP / 16][4];
+    {
+        const __nv_bfloat16* q_lo = a.q + ((long long)(tok0 + qi) * a.n_heads + head) * hd + 2 * t;
+        const __nv_bfloat16* q_hi = q_lo + 8 * (long long)a.n_heads * hd;
+        const bool lo_ok = qi < n_new, hi_ok = qi + 8 < n_new;
+#pragma unroll
+        for (int ks = 0; ks < HDP / 16; ++ks) {
+            const bool c0 = 16 * ks + 2 * t < hd, c1 = 16 * ks + 8 + 2 * t < hd;
+            qa[ks][0] = lo_ok && c0 ? *reinterpret_cast<const uint32_t*>(q_lo + 16 * ks) : 0u;
+            qa[ks][1] = hi_ok && c0 ? *reinterpret_cast<const uint32_t*>(q_hi + 16 * ks) : 0u;
+            qa[ks][2] = lo_ok && c1 ? *reinterpret_cast<const uint32_t*>(q_lo + 16 * ks + 8) : 0u;
+            qa[ks][3] = hi_ok && c1 ? *reinterpret_cast<const uint32_t*>(q_hi + 16 * ks + 8) : 0u;
+        }
+    }
+    const uint32_t k_lane = (uint32_t)((((lane >> 4) * 8 + (lane & 7)) * CPRK) * 16);
+    const uint32_t v_lane = (uint32_t)(((((lane >> 3) & 1) * 8 + (lane & 7)) * CPRV) * 16);
+    uint32_t k_col[HDP / 16], v_col[VDP / 16];
+#pragma unroll
+    for (int i = 0; i < HDP / 16; ++i) k_col[i] = (uint32_t)(((2 * i + ((lane >> 3) & 1)) ^ (lane & 7)) * 16);
+#pragma unroll
+    for (int i = 0; i < VDP / 16; ++i) v_col[i] = (uint32_t)(((2 * i + (lane >> 4)) ^ (lane & 7)) * 16);
+
+    for (int kt = kt_begin; kt <= kt_end; ++kt) {
+        const int buf = (kt - kt_begin) & 1;
+        if (kt < kt_end) {                                        // prefetch the next tile
+            load_tile(kt + 1, buf ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+
+        // S[16][64] = Q K^T
+        float s[8][4];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f; }
+        const uint32_t ks_base = k_s + (uint32_t)(buf * 64 * HDP * 2) + k_lane;
+#pragma unroll
+        for (int ks = 0; ks < HDP / 16; ++ks) {
+#pragma unroll
+            for (int np = 0; np < 4; ++np) {                      // pairs of 8-key tiles
+                uint32_t b0, b1, b2, b3;
+                sm_ldsm_x4(ks_base + k_col[ks] + (uint32_t)(np * 16 * CPRK * 16), b0, b1, b2, b3);
+                sm_mma16816(s[2 * np], qa[ks], b0, b1);
+                sm_mma16816(s[2 * np + 1], qa[ks], b2, b3);
+            }
+        }
+
+        // scale, bias by distance, mask by position
+        const int key0 = kt * SM_KEYS;
+        const bool all_visible = key0 >= warp_lo_max && key0 + SM_KEYS - 1 <= pos0 + warp * 16;
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = key0 + nt * 8 + 2 * t + (e & 1);
+                const int r = e >> 1;
+                const int d = row_p[r] - key;
+                float x = s[nt][e] * a.scale_log2;
+                const bool vis = all_visible || (d >= 0 && key >= row_lo[r]);
+                if (has_bias && vis)
+                    x -= a.tab_n > 0 ? tab[d] : r1 * __log2f(fmaf(r2, (float)d, 1.0f));
+                s[nt][e] = vis ? x : -INFINITY;
+            }
+        }
+        // online softmax (base 2)
+        float m_new[2] = {m_r[0], m_r[1]};
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+            m_new[0] = fmaxf(m_new[0], fmaxf(s[nt][0], s[nt][1]));
+            m_new[1] = fmaxf(m_new[1], fmaxf(s[nt][2], s[nt][3]));
+        }
+        float corr[2], m_use[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            m_new[r] = fmaxf(m_new[r], __shfl_xor_sync(0xffffffffu, m_new[r], 1));
+            m_new[r] = fmaxf(m_new[r], __shfl_xor_sync(0xffffffffu, m_new[r], 2));
+            // a row with nothing visible yet keeps m = -inf; 0 as its offset gives
+            // exp2(-inf - 0) = 0 and no inf - inf
+            m_use[r] = m_new[r] == -INFINITY ? 0.0f : m_new[r];
+            corr[r] = m_r[r] == -INFINITY ? 0.0f : exp2f(m_r[r] - m_use[r]);
+            m_r[r] = m_new[r];
+            l_r[r] *= corr[r];
+        }
+#pragma unroll
+        for (int i = 0; i < VDP / 8; ++i) {
+            o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1];
+        }
+        uint32_t pa[4][4];
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+            float p[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                p[e] = exp2f(s[nt][e] - m_use[e >> 1]);
+                l_r[e >> 1] += p[e];
+            }
+            pa[nt >> 1][(nt & 1) * 2 + 0] = sm_pack2(p[0], p[1]);
+            pa[nt >> 1][(nt & 1) * 2 + 1] = sm_pack2(p[2], p[3]);
+        }
+        // O += P V
+        const uint32_t vs_base = v_s + (uint32_t)(buf * 64 * VDP * 2) + v_lane;
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+#pragma unroll
+            for (int np = 0; np < VDP / 16; ++np) {
+                uint32_t r0, r1_, r2_, r3;
+                sm_ldsm_x4_trans(vs_base + v_col[np] + (uint32_t)(ks * 16 * CPRV * 16), r0, r1_, r2_, r3);
+                sm_mma16816(o[2 * np], pa[ks], r0, r1_);
+                sm_mma16816(o[2 * np + 1], pa[ks], r2_, r3);
+            }
+        }
+        __syncthreads();                                          // the buffer may be refilled now
+    }
+
+    float inv[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l_r[r] += __shfl_xor_sync(0xffffffffu, l_r[r], 1);
+        l_r[r] += __shfl_xor_sync(0xffffffffu, l_r[r], 2);
+        if (a.sink) l_r[r] += exp2f(-m_r[r]);
+        inv[r] = 1.0f / l_r[r];
+    }
+#pragma unroll
+    for (int nt = 0; nt < VDP / 8; ++nt) {
+        const int d = nt * 8 + 2 * t;
+        if (d < vd) {
+            if (qi < n_new)
+                *reinterpret_cast<uint32_t*>(a.out + ((long long)(tok0 + qi) * a.n_heads + head) * vd + d) =
+                    sm_pack2(o[nt][0] * inv[0], o[nt][1] * inv[0]);
+            if (qi + 8 < n_new)
+                *reinterpret_cast<uint32_t*>(a.out + ((long long)(tok0 + qi + 8) * a.n_heads + head) * vd + d) =
+                    sm_pack2(o[nt][2] * inv[1], o[nt][3] * inv[1]);
+        }
+    }
+}
+
+template <int HDP, int VDP, bool PAGED>
+static int launch_sink_mma(const SinkMmaArgs& a, int n_seqs, int max_new, cudaStream_t stream) {
+    const int smem = 2 * 64 * (HDP + VDP) * 2 + a.tab_n * 4;
+    static int configured = 0;
+    if (configured < smem) {
+        cudaError_t e = cudaFuncSetAttribute(sink_attention_mma_kernel<HDP, VDP, PAGED>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             2 * 64 * (HDP + VDP) * 2 + SM_MAX_TAB * 4);
+        if (e != cudaSuccess) return (int)e;
+        configured = 2 * 64 * (HDP + VDP) * 2 + SM_MAX_TAB * 4;
+    }
+    dim3 grid((max_new + SM_ROWS - 1) / SM_ROWS, a.n_heads, n_seqs);
+    mf_launch(sink_attention_mma_kernel<HDP, VDP, PAGED>, grid, dim3(SM_WARPS * 32), (size_t)smem,
+              stream, a);
+    return MF_LAUNCH_CHECK();
+}
+
+// 1 if the tensor-core kernels take these sizes (bfloat16 only)
+extern "C" int mf_sink_attention_mma_supported(int hd, int vd) {
+    return hd >= 8 && vd >= 8 && hd <= 128 && vd <= 128 && hd % 8 == 0 && vd % 8 == 0;
+}
+
+// q [tokens][n_heads][hd] bfloat16, the step's packed rows; sequence b brings the tokens
+// cu_seqlens[b] .. cu_seqlens[b+1]-1.  `page_table` null: keys and values are the step's own
+// packed rows and every sequence starts at position 0; else they come from the cache and
+// sequence b ends at seq_end[b] after this step.
+extern "C" int mf_sink_attention_mma(const void* q, const void* k, const void* v,
+                                     const int* cu_seqlens, const int* seq_end,
+                                     const int* page_table, int table_stride, int ring, void* out,
+                                     const float* r1, const float* r2, int n_seqs, int max_new,
+                                     int n_heads, int n_kv, int hd, int vd, int window, int chunk,
+                                     int sink, float scale, cudaStream_t stream) {
+    if (n_seqs <= 0 || max_new <= 0) return 0;
+    if (!mf_sink_attention_mma_supported(hd, vd) || n_kv <= 0 || n_heads % n_kv != 0) return MF_ERR_UNSUPPORTED;
+    if (n_heads > 65535 || n_seqs > 65535 || window < 0 || chunk < 0) return MF_ERR_UNSUPPORTED;
+    if ((page_table == nullptr) != (seq_end == nullptr)) return MF_ERR_ARGUMENT;
+    if (((uintptr_t)q & 15) || ((uintptr_t)k & 15) || ((uintptr_t)v & 15)) return MF_ERR_UNSUPPORTED;
+    SinkMmaArgs a;
+    a.q = (const __nv_bfloat16*)q; a.k = (const __nv_bfloat16*)k; a.v = (const __nv_bfloat16*)v;
+    a.cu_seqlens = cu_seqlens; a.seq_end = seq_end; a.page_table = page_table;
+    a.table_stride = table_stride; a.ring = ring; a.out = (__nv_bfloat16*)out; a.r1 = r1; a.r2 = r2;
+    a.n_heads = n_heads; a.n_kv = n_kv; a.hd = hd; a.vd = vd; a.window = window; a.chunk = chunk;
+    a.sink = sink ? 1 : 0;
+    int reach = 0;
+    if (chunk > 0) reach = chunk;
+    if (window > 0 && (reach == 0 || window < reach)) reach = window;
+    a.tab_n = (r1 != nullptr && reach > 0 && reach <= SM_MAX_TAB) ? reach : 0;
+    a.scale_log2 = scale * 1.4426950408889634f;
+    const bool paged = page_table != nullptr;
+#define MF_SINK_MMA(H, V) \
+    (paged ? launch_sink_mma<H, V, true>(a, n_seqs, max_new, stream) \
+           : launch_sink_mma<H, V, false>(a, n_seqs, max_new, stream))
+    if (hd <= 64) return vd <= 64 ? MF_SINK_MMA(64, 64) : MF_SINK_MMA(64, 128);
+    return vd <= 64 ? MF_SINK_MMA(128, 64) : MF_SINK_MMA(128, 128);
+#undef MF_SINK_MMA
 }

@@ -46,6 +46,8 @@
 #define EPI_ACCUM 1           // out += acc + bias         (float32)
 #define EPI_SWIGLU 2          // rows of W interleaved gate,up: out[j] = silu(g) * u (bfloat16)
 #define EPI_PARTIAL 3         // ws[split][token][n] = acc (float32)
+#define EPI_XIELU 4           // out = f(acc + bias), f(z) = act_p z^2 + z/2 (z > 0),
+                              // act_n (exp(z) - 1 - z) + z/2 (z <= 0)   (float32 or bfloat16)
 
 #define MF_ERR_NO_TENSORMAP 2003
 #define MF_ERR_TENSORMAP 2004
@@ -71,7 +73,13 @@ struct GemmArgs {
     const float* prep_g;
     float* prep_ssq;
     long long ldp;            // elements between consecutive tokens of prep_x
+    float act_p, act_n;       // EPI_XIELU: the two coefficients of the activation
 };
+
+// an epilogue that is not linear in the accumulator cannot run on a K split's partial sums
+__host__ __device__ constexpr bool epi_needs_whole_sum(int epi) {
+    return epi == EPI_SWIGLU || epi == EPI_XIELU;
+}
 
 // 1 / rms of the token rows m0 + t, t = first, first + step, .. < n_tok, into out[t] (shared
 // memory): a thread adds a token's parts in order, all of its loads in flight together.
@@ -242,7 +250,10 @@ __device__ __forceinline__ void store_chunk(const GemmArgs& a, const uint32_t* r
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
             const int tok = tok0 + j;
-            const float v = __uint_as_float(r[j]) + bias;
+            float v = __uint_as_float(r[j]) + bias;
+            if (a.epi == EPI_XIELU)
+                v = v > 0.0f ? fmaf(a.act_p * v, v, 0.5f * v)
+                             : fmaf(a.act_n, (__expf(v) - 1.0f) - v, 0.5f * v);
             if (tok < a.M && n_ok) {
                 if (a.epi == EPI_PARTIAL)
                     a.partial[((size_t)split * a.M + tok) * a.N + n] = v;
@@ -1137,7 +1148,7 @@ extern "C" int mf_gemm_tc_plan(int M, int N, int K, int epi, int* token_tile, in
     const int kblocks = (K + TILE_K - 1) / TILE_K;
     int s = 1;
     const long long weight_bytes = (long long)N * K * 2;
-    if (epi != EPI_SWIGLU && nt <= 64 && weight_bytes <= (16ll << 20)) {
+    if (!epi_needs_whole_sum(epi) && nt <= 64 && weight_bytes <= (16ll << 20)) {
         // small weights (up to 16 MB): their bytes cost next to nothing, the chain of loads of
         // one CTA does (it has STAGES tiles in flight and waits a round trip for each refill).
         // So K is cut until a CTA has 2 k-blocks and asks for all of its weight tiles at once,
@@ -1149,7 +1160,7 @@ extern "C" int mf_gemm_tc_plan(int M, int N, int K, int epi, int* token_tile, in
         if (s > kblocks / 2) s = kblocks / 2;
         if (s > 16) s = 16;
         if (s < 1) s = 1;
-    } else if (epi != EPI_SWIGLU && tiles < 200 && kblocks >= 8) {
+    } else if (!epi_needs_whole_sum(epi) && tiles < 200 && kblocks >= 8) {
         // up to two CTAs per SM (the small-token kernels are sized for that), each with at
         // least 4 k-blocks; the partial sums (written and read once) stay under half of the
         // weight bytes: splits * M * N * 8 <= N * K  =>  splits <= K / (8 M)
@@ -1180,6 +1191,7 @@ struct FusedNorm {
     long long ldp;
     const float* prep_g;      // ... its weight [N] ...
     float* prep_ssq;          // ... and the sums of squares [parts][M] this product writes
+    float act_p = 0.0f, act_n = 0.0f;   // EPI_XIELU
 };
 
 static int pair_mode_on() {
@@ -1216,7 +1228,7 @@ static int gemm_tc_impl(const void* x, long long ldx, const void* w, long long l
     if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return MF_ERR_UNSUPPORTED;
     if (epi == EPI_ACCUM && out_dtype != MF_DTYPE_F32) return MF_ERR_UNSUPPORTED;
     if (epi == EPI_SWIGLU && (out_dtype != MF_DTYPE_BF16 || N % 2 != 0)) return MF_ERR_UNSUPPORTED;
-    if (epi < EPI_STORE || epi > EPI_SWIGLU) return MF_ERR_ARGUMENT;
+    if (epi != EPI_STORE && epi != EPI_ACCUM && epi != EPI_SWIGLU && epi != EPI_XIELU) return MF_ERR_ARGUMENT;
     const bool prep = f != nullptr && f->prep_x != nullptr;
     if (prep && (epi != EPI_ACCUM || f->prep_g == nullptr || f->prep_ssq == nullptr)) return MF_ERR_ARGUMENT;
     if (f != nullptr && f->row_ssq != nullptr && (f->ssq_parts <= 0 || f->ssq_width <= 0)) return MF_ERR_ARGUMENT;
@@ -1232,6 +1244,7 @@ static int gemm_tc_impl(const void* x, long long ldx, const void* w, long long l
     if (f != nullptr) {
         a.row_ssq = f->row_ssq; a.ssq_parts = f->ssq_parts; a.ssq_width = f->ssq_width; a.ssq_eps = f->ssq_eps;
         a.prep_x = f->prep_x; a.ldp = f->ldp; a.prep_g = f->prep_g; a.prep_ssq = f->prep_ssq;
+        a.act_p = f->act_p; a.act_n = f->act_n;
     }
     if (pair_mode_on() && M >= 256 && splits == 1) {
         if (a.row_ssq != nullptr) return MF_ERR_UNSUPPORTED;     // the CTA-pair kernel applies no row scale
@@ -1330,6 +1343,22 @@ extern "C" int mf_gemm_tc_fused(const void* x, long long ldx, const void* w, lon
     f.prep_x = (__nv_bfloat16*)prep_x; f.ldp = ldp; f.prep_g = prep_g; f.prep_ssq = prep_ssq;
     return gemm_tc_impl(x, ldx, w, ldw, bias, out, ldo, out_dtype, M, N, K, epi, workspace, deferred,
                         status, &f, stream);
+}
+
+// out = f(x w^T) with the xIELU activation f(z) = act_p z^2 + z/2 (z > 0), act_n (exp(z) - 1 - z)
+// + z/2 (z <= 0) applied to the float32 sums in the epilogue (never split along K); `row_ssq`
+// as in mf_gemm_tc_fused.
+extern "C" int mf_gemm_tc_xielu(const void* x, long long ldx, const void* w, long long ldw,
+                                void* out, long long ldo, int out_dtype, int M, int N, int K,
+                                float act_p, float act_n, const float* row_ssq, int ssq_parts,
+                                int ssq_width, float ssq_eps, unsigned* status,
+                                cudaStream_t stream) {
+    FusedNorm f;
+    f.row_ssq = row_ssq; f.ssq_parts = ssq_parts; f.ssq_width = ssq_width; f.ssq_eps = ssq_eps;
+    f.prep_x = nullptr; f.ldp = 0; f.prep_g = nullptr; f.prep_ssq = nullptr;
+    f.act_p = act_p; f.act_n = act_n;
+    return gemm_tc_impl(x, ldx, w, ldw, nullptr, out, ldo, out_dtype, M, N, K, EPI_XIELU, nullptr,
+                        nullptr, status, &f, stream);
 }
 
 // out (+)= bias + sum over the K splits left in `partial` ([splits][M][N]) by a deferred

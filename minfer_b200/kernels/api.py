@@ -133,6 +133,11 @@ def _sig_attention_sink(lib: ctypes.CDLL) -> None:
                                             [c_int] * 8 + [c_float, c_int, c_void_p])
 
 
+    lib.mf_sink_attention_mma_supported.argtypes = [c_int, c_int]
+    lib.mf_sink_attention_mma.argtypes = ([c_void_p] * 6 + [c_int, c_int] + [c_void_p] * 3 +
+                                          [c_int] * 9 + [c_float, c_void_p])
+
+
 def _sig_sampling(lib: ctypes.CDLL) -> None:
     lib.mf_sample.argtypes = [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p,
                               c_void_p, c_float, c_int, c_float, c_float, c_float, c_float,
@@ -158,6 +163,9 @@ def _sig_gemm_tc(lib: ctypes.CDLL) -> None:
                                      c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                      c_void_p, c_int, c_int, c_float, c_void_p, c_longlong, c_void_p,
                                      c_void_p, c_void_p, c_void_p]
+    lib.mf_gemm_tc_xielu.argtypes = [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong,
+                                     c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_int,
+                                     c_int, c_float, c_void_p, c_void_p]
     lib.mf_gemm_tc_prep_parts.argtypes = [c_int, c_int, c_int]
     lib.mf_wait_probe.argtypes = [c_void_p, ctypes.c_uint, c_ulonglong, c_void_p, c_void_p]
 
@@ -435,6 +443,29 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out:
                           out.data_ptr(), out.stride(0), dtype_code(out.dtype), m, n, k, epi,
                           _ptr(ws, "workspace"), None, _i32(status, "status"), _stream()),
            "gemm_tc", 2 if need else 1)
+
+
+def gemm_tc_xielu(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, act_p: float, act_n: float,
+                  status: torch.Tensor, row_scale: Optional["RowScale"] = None) -> None:
+    """out = f(x @ w^T) on tcgen05, f the xIELU activation with its two coefficients
+    (act_p = softplus(a0), act_n = 1/2 + softplus(a1)) applied to the float32 sums in the
+    product's epilogue.  ``row_scale`` as in ``gemm_tc_fused``."""
+    m, k = x.shape
+    n = w.shape[0]
+    if w.shape[1] != k or out.shape != (m, n) or out.stride(1) != 1:
+        raise KernelError(f"gemm: shapes do not fit: x {tuple(x.shape)}, w {tuple(w.shape)}, "
+                          f"out {tuple(out.shape)}")
+    if not gemm_tc_supported(x, w):
+        raise KernelError("gemm_tc: operands must be bfloat16 with 16-byte aligned rows")
+    rs = row_scale
+    if rs is not None and (rs.ssq.dim() != 2 or rs.ssq.shape[1] != m):
+        raise KernelError("gemm: the sums of squares must be [parts, rows]")
+    _check(_lib("gemm_tc").mf_gemm_tc_xielu(
+        x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
+        dtype_code(out.dtype), m, n, k, float(act_p), float(act_n),
+        _f32(rs.ssq, "ssq") if rs is not None else None, rs.ssq.shape[0] if rs is not None else 0,
+        rs.width if rs is not None else 0, rs.eps if rs is not None else 0.0,
+        _i32(status, "status"), _stream()), "gemm_tc_xielu")
 
 
 class RowScale:
@@ -747,6 +778,35 @@ def sink_attention_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
         _ptr(out, "out"), _f32(r1, "r1"), _f32(r2, "r2"), rows, n_heads, n_kv, head_dim, value_dim,
         int(window), int(chunk), 1 if sink else 0, float(scale), dtype_code(q.dtype), _stream()),
         "sink_attention_paged")
+
+
+def sink_attention_mma_supported(dtype: torch.dtype, head_dim: int, value_dim: int) -> bool:
+    """The tensor-core kernels of this attention take bfloat16 with key and value sizes that are
+    multiples of 8 up to 128."""
+    return (dtype == torch.bfloat16 and
+            bool(_lib("attention_sink").mf_sink_attention_mma_supported(int(head_dim), int(value_dim))))
+
+
+def sink_attention_mma(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: torch.Tensor,
+                       seq_end: Optional[torch.Tensor], page_table: Optional[torch.Tensor],
+                       table_stride: int, ring: int, out: torch.Tensor, r1: Optional[torch.Tensor],
+                       r2: Optional[torch.Tensor], n_rows: int, max_row_tokens: int, n_heads: int,
+                       n_kv: int, head_dim: int, value_dim: int, window: int, chunk: int, sink: bool,
+                       scale: float) -> None:
+    """The step's packed queries (sequence b brings tokens cu_seqlens[b] .. cu_seqlens[b+1]-1)
+    on tensor cores.  ``page_table`` None: ``k``, ``v`` are the step's own packed rows and every
+    sequence starts at position 0; else they are the cache and sequence b ends at
+    ``seq_end[b]`` after the step."""
+    if q.dtype != torch.bfloat16 or out.shape != (q.shape[0], n_heads * value_dim):
+        raise KernelError("sink_attention_mma: bfloat16 only, out [tokens, heads * value size]")
+    if (r1 is None) != (r2 is None) or (page_table is None) != (seq_end is None):
+        raise KernelError("sink_attention_mma: inconsistent arguments")
+    _check(_lib("attention_sink").mf_sink_attention_mma(
+        _ptr(q, "q"), _ptr(k, "k"), _ptr(v, "v"), _i32(cu_seqlens, "cu_seqlens"),
+        _i32(seq_end, "seq_end"), _i32(page_table, "page_table"), int(table_stride), int(ring),
+        _ptr(out, "out"), _f32(r1, "r1"), _f32(r2, "r2"), int(n_rows), int(max_row_tokens), n_heads,
+        n_kv, head_dim, value_dim, int(window), int(chunk), 1 if sink else 0, float(scale),
+        _stream()), "sink_attention_mma")
 
 
 def sampler_state_ints() -> int:

@@ -8,6 +8,7 @@ the down projection adds into the residual stream in its epilogue.
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Optional
 
 import torch
@@ -105,6 +106,10 @@ class GatedMlp(FeedForward):
             ctx.extras["pending"] = pending
 
 
+# MINFER_B200_FUSE_ACTIVATION=0: the dense feed-forward's activation runs as a kernel of its own
+FUSE_ACTIVATION = os.environ.get("MINFER_B200_FUSE_ACTIVATION", "1") != "0"
+
+
 class DenseMlp(FeedForward):
     """Feed-forward without a gate: down( act(up(x)) ), no biases.  ``activation``:
 
@@ -149,15 +154,26 @@ class DenseMlp(FeedForward):
         self.down = Linear(weights[f"{prefix}{self.down_name}"])
         self.act_params = weights[f"{prefix}{self.act_name}"]
         self.accepts_row_scale = self.up.takes_row_scale()
+        # the activation's two coefficients, once, for the product whose epilogue applies it
+        a = self.act_params.detach().to("cpu", torch.float64)
+        sp = torch.log1p(torch.exp(-a.abs())) + torch.clamp(a, min=0)
+        self._act_p, self._act_n = float(sp[0]), 0.5 + float(sp[1])
 
     def export(self, prefix: str) -> Dict[str, torch.Tensor]:
         return {f"{prefix}{self.up_name}": self.up.weight, f"{prefix}{self.down_name}": self.down.weight,
                 f"{prefix}{self.act_name}": self.act_params}
 
     def forward_add(self, x: torch.Tensor, ctx: StepContext, residual: torch.Tensor) -> None:
+        from ..kernels import gemm
         act = torch.empty((x.shape[0], self.intermediate_size), dtype=ctx.act_dtype, device=x.device)
-        z = self.up.forward(x, torch.float32, row_scale=ctx.input_scale)
-        K.xielu(z, self.act_params, act)
+        if (x.shape[0] > 0 and self.up.takes_row_scale() and x.dtype == torch.bfloat16
+                and K.gemm_tc_supported(x, self.up.weight) and FUSE_ACTIVATION):
+            # the activation rides on the up projection's epilogue
+            K.gemm_tc_xielu(x, self.up.weight, act, self._act_p, self._act_n,
+                            gemm.status_word(x.device), row_scale=ctx.input_scale)
+        else:
+            z = self.up.forward(x, torch.float32, row_scale=ctx.input_scale)
+            K.xielu(z, self.act_params, act)
         target = ctx.extras.pop("prepare_for", None)
         if target is not None:
             settle_pending(ctx, residual)

@@ -18,6 +18,7 @@ ring of that many positions plus what a step may add, as for a windowed layer.
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Optional
 
 import torch
@@ -26,6 +27,14 @@ from ..kernels import api as K
 from ..weights.spec import MATRIX, VECTOR, Init, TensorSpec
 from .base import CacheRequest, CallBinding, Mixer, StepContext, settle_pending
 from .linear import Linear
+
+
+# MINFER_B200_SINK_ATTENTION_GENERIC=1: every step takes the generic kernel (for comparison)
+FORCE_GENERIC = os.environ.get("MINFER_B200_SINK_ATTENTION_GENERIC", "0") == "1"
+# a step that is neither whole prompts nor one token a row runs the query-tile kernel over the
+# cache's pages from this many tokens on; below, every token is a row of the kernel for single
+# queries
+PAGED_PROMPT_MIN_TOKENS = int(os.environ.get("MINFER_B200_SINK_PAGED_PROMPT_MIN_TOKENS", "48"))
 
 
 class SinkAttention(Mixer):
@@ -149,7 +158,12 @@ class SinkAttention(Mixer):
                             nh, nk, hd, vd, self.norm_eps, self.qk_norm, ctx.status,
                             n_partials=n_partials)
         o = torch.empty((n, nh * vd), dtype=act, device=dev)
-        if own_kv:
+        tensor_cores = (K.sink_attention_mma_supported(act, hd, vd) and not FORCE_GENERIC)
+        if own_kv and tensor_cores:
+            K.sink_attention_mma(q, k_step, v_step, ctx.cu_seqlens, None, None, 0, 0, o, self.r1,
+                                 self.r2, ctx.n_rows, ctx.max_row_tokens, nh, nk, hd, vd,
+                                 self.window, self.chunk, self.sink, self.scale)
+        elif own_kv:
             K.sink_attention_packed(q, k_step, v_step, ctx.token_row, ctx.positions,
                                     ctx.cu_seqlens, o, self.r1, self.r2, nh, nk, hd, vd,
                                     self.window, self.chunk, self.sink, self.scale)
@@ -160,6 +174,14 @@ class SinkAttention(Mixer):
                     f"a sequence brings {ctx.max_row_tokens} tokens, but a ring of {cache.ring} "
                     f"positions with a reach of {reach} takes {cache.ring - reach + 1} a step "
                     f"(the engine runs longer rows in portions)")
+            if tensor_cores and not ctx.single_token and ctx.n_tokens >= PAGED_PROMPT_MIN_TOKENS:
+                # rows of several tokens: query tiles of the step's rows over the cache's pages
+                K.sink_attention_mma(q, cache.k, cache.v, ctx.cu_seqlens, ctx.seq_end,
+                                     cache.page_table, cache.table_stride, cache.ring, o, self.r1,
+                                     self.r2, ctx.n_rows, ctx.max_row_tokens, nh, nk, hd, vd,
+                                     self.window, self.chunk, self.sink, self.scale)
+                self._project_out(o, ctx, residual)
+                return
             K.sink_attention_paged(q, cache.k, cache.v, ctx.token_row, ctx.positions,
                                    cache.page_table, cache.table_stride, cache.ring, o, self.r1,
                                    self.r2, nh, nk, hd, vd, self.window, self.chunk, self.sink,

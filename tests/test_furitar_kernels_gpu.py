@@ -277,3 +277,90 @@ def test_unit_norm_and_cache_write(dtype, splits):
         page = pages[b][p // 64]
         assert torch.equal(kc[page, :, p % 64], k_out[i]) and torch.equal(vc[page, :, p % 64], v_out[i])
     assert float(kc[3].abs().max()) == 0.0 and float(kc[2, :, 6:].abs().max()) == 0.0
+
+
+# ---------------------------------------------------------------------------------------------
+# the tensor-core kernels (bfloat16)
+# ---------------------------------------------------------------------------------------------
+MMA_CASES = [  # heads, kv, hd, vd, chunk, lengths
+    (8, 2, 64, 64, 200, [401, 200, 201, 1]),
+    (16, 1, 64, 128, 150, [310, 64]),
+    (4, 4, 128, 128, 128, [129, 257]),
+    (6, 2, 48, 80, 96, [333, 95, 97]),
+    (2, 1, 128, 40, 64, [191]),
+    (4, 2, 8, 8, 1, [70]),
+    (3, 1, 104, 56, 0, [500, 17]),
+    (4, 2, 64, 64, 5000, [300]),
+]
+
+
+@pytest.mark.parametrize("case", MMA_CASES)
+@pytest.mark.parametrize("bias, sink", [(True, True), (False, True), (True, False)])
+def test_prompt_kernel_on_tensor_cores_packed(case, bias, sink):
+    heads, kv, hd, vd, chunk, lengths = case
+    q, k, v, r1, r2 = _qkv_case(hd + 2 * vd, heads, kv, hd, vd, lengths)
+    _spike(q, k, v, lengths, chunk, heads // kv)
+    if not bias:
+        r1 = r2 = torch.zeros(heads, dtype=torch.float64)
+    t = torch.bfloat16
+    qd, kd, vd_ = q.to(t).to(DEV), k.to(t).to(DEV), v.to(t).to(DEV)
+    want = _plain_rows(qd.double().cpu(), kd.double().cpu(), vd_.double().cpu(), r1, r2, 0.3, chunk, lengths)
+    if not sink:
+        ones = _plain_rows(qd.double().cpu(), kd.double().cpu(), torch.ones_like(vd_).double().cpu(), r1,
+                           r2, 0.3, chunk, lengths)
+        want = (want.view(-1, heads, vd) / ones.view(-1, heads, vd)[..., :1]).reshape(want.shape)
+    cu = [0]
+    for n in lengths:
+        cu.append(cu[-1] + n)
+    out = torch.empty(sum(lengths), heads * vd, dtype=t, device=DEV)
+    f = lambda x: x.float().to(DEV) if bias else None
+    assert K().sink_attention_mma_supported(t, hd, vd)
+    K().sink_attention_mma(qd, kd, vd_, _i32(cu), None, None, 0, 0, out, f(r1), f(r2), len(lengths),
+                           max(lengths), heads, kv, hd, vd, 0, chunk, sink, 0.3)
+    assert _err(out, want) < 2e-2
+
+
+@pytest.mark.parametrize("case", MMA_CASES)
+@pytest.mark.parametrize("ringed", [False, True])
+def test_prompt_kernel_on_tensor_cores_over_pages(case, ringed):
+    """The last positions of every sequence as one step's rows over the paged cache."""
+    heads, kv, hd, vd, chunk, lengths = case
+    if ringed and (chunk == 0 or chunk > 1000):
+        pytest.skip("a ring needs a bound on how far a query looks back")
+    q, k, v, r1, r2 = _qkv_case(5 * hd + vd, heads, kv, hd, vd, lengths)
+    _spike(q, k, v, lengths, chunk, heads // kv)
+    t = torch.bfloat16
+    qd, kd, vd_ = q.to(t), k.to(t), v.to(t)
+    want_all = _plain_rows(qd.double(), kd.double(), vd_.double(), r1, r2, 0.3, chunk, lengths)
+    tail_max = 70
+    ring = -(-(chunk + tail_max - 1) // 64) * 64 if ringed else 0
+    kc, vc, table, stride = _paged(kd, vd_, lengths, ring, seed=vd)
+    rows, cu, at = [], [0], 0
+    for n in lengths:
+        tail = min(n, tail_max)
+        rows += list(range(at + n - tail, at + n))
+        cu.append(cu[-1] + tail)
+        at += n
+    out = torch.empty(len(rows), heads * vd, dtype=t, device=DEV)
+    K().sink_attention_mma(qd[rows].contiguous().to(DEV), kc.to(DEV), vc.to(DEV), _i32(cu),
+                           _i32(lengths), table.reshape(-1).to(DEV), stride, ring, out,
+                           r1.float().to(DEV), r2.float().to(DEV), len(lengths), tail_max, heads, kv,
+                           hd, vd, 0, chunk, True, 0.3)
+    assert _err(out, want_all[rows]) < 2e-2
+
+
+def test_xielu_in_the_products_epilogue():
+    """The up projection with the activation in its epilogue against product, then activation."""
+    g = torch.Generator().manual_seed(4)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for m, n, k in ((5, 136, 72), (64, 256, 256), (300, 384, 128), (1000, 512, 264)):
+        x = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+        w = (0.2 * torch.randn(n, k, generator=g)).to(torch.bfloat16).to(DEV)
+        a = torch.tensor([0.4, -0.3], dtype=torch.float64)
+        sp = P.softplus(a)
+        for out_dtype in (torch.bfloat16, torch.float32):
+            out = torch.empty(m, n, dtype=out_dtype, device=DEV)
+            K().gemm_tc_xielu(x, w, out, float(sp[0]), 0.5 + float(sp[1]), status)
+            want = P.xielu(x.double().cpu() @ w.double().cpu().T, a)
+            assert _err(out, want) < (1.2e-2 if out_dtype == torch.bfloat16 else 2e-4)
+    assert int(status.item()) == 0

@@ -703,3 +703,351 @@ extern "C" int mf_sink_attention_mma(const void* q, const void* k, const void* v
     return vd <= 64 ? MF_SINK_MMA(128, 64) : MF_SINK_MMA(128, 128);
 #undef MF_SINK_MMA
 }
+
+// ------------------------------------------------------------------------------------------
+// Single queries over the paged cache on tensor cores (bfloat16; sizes as above; up to 16
+// query heads per key/value head).
+//
+// One CTA owns (key split, key/value head, query).  The query heads of the key/value head are
+// the 16 rows of an m16n8k16 MMA, so a key or value is read once for the whole group.  The
+// keys a query sees, [first visible, position], are cut into tiles of 32 absolute positions (a
+// tile lies in one page); a CTA takes `tiles_per_cta` consecutive tiles, its four warps take
+// every fourth of them, each with a double buffer of its own in shared memory (cp.async, XOR
+// swizzle) and its own running maximum, sum and output.  The warps' results are merged in
+// shared memory in warp order.  One split: the output is written (the sink added).  Several:
+// a partial (maximum, sum, output) per split, merged by sink_decode_combine_kernel in split
+// order, which adds the sink.  Base-2 exponentials throughout.
+// ------------------------------------------------------------------------------------------
+#define SD_WARPS 4
+#define SD_KEYS 32
+
+struct SinkDecodeArgs {
+    const __nv_bfloat16* q;   // [rows][n_heads][hd]
+    const __nv_bfloat16* k;   // cache [pages][n_kv][64][hd]
+    const __nv_bfloat16* v;   // cache [pages][n_kv][64][vd]
+    const int* row_seq;       // [rows] batch row of each query
+    const int* row_pos;       // [rows] absolute position of each query
+    const int* page_table;
+    int table_stride, ring;
+    __nv_bfloat16* out;       // [rows][n_heads * vd]
+    float* partial;           // [rows][n_heads][n_splits][vd + 2]   (n_splits > 1)
+    const float* r1;
+    const float* r2;
+    int n_heads, n_kv, hd, vd, window, chunk, sink;
+    int tiles_per_cta, n_splits;
+    float scale_log2;
+};
+
+// a warp copies 32 rows of `d` elements (row r at base + r * d) into its swizzled [32][DP] tile
+template <int DP>
+__device__ __forceinline__ void sd_copy_tile(uint32_t tile, const __nv_bfloat16* base, int d,
+                                             int lane) {
+    constexpr int CPR = DP / 8;
+#pragma unroll
+    for (int i = 0; i < CPR; ++i) {
+        const int idx = lane + 32 * i;
+        const int r = idx / CPR, c = idx % CPR;
+        const bool ok = c * 8 < d;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+                     ::"r"(tile + (uint32_t)((r * CPR + (c ^ (r & 7))) * 16)),
+                       "l"(ok ? base + (long long)r * d + c * 8 : base), "r"(ok ? 16 : 0)
+                     : "memory");
+    }
+}
+
+template <int HDP, int VDP>
+__global__ void __launch_bounds__(SD_WARPS * 32) sink_attention_decode_kernel(SinkDecodeArgs a) {
+    pdl_launch_dependents();
+    constexpr int CPRK = HDP / 8, CPRV = VDP / 8;
+    constexpr int TILE_BYTES = SD_KEYS * (HDP + VDP) * 2;          // one buffer: K then V
+    constexpr int OS = VDP + 4;                                    // padded row of a warp's output
+    extern __shared__ __align__(128) uint8_t sd_smem[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int split = blockIdx.x, hk = blockIdx.y, row = blockIdx.z;
+    const int G = a.n_heads / a.n_kv;
+    const int hd = a.hd, vd = a.vd;
+    const int b = a.row_seq[row];
+    const int pos = a.row_pos[row];
+    const int lo = sink_first_key(pos, a.window, a.chunk);
+    const int tile_lo = lo / SD_KEYS + split * a.tiles_per_cta;   // this CTA's first tile
+    const int tile_hi = min(pos / SD_KEYS, tile_lo + a.tiles_per_cta - 1);   // inclusive
+    const bool has_bias = a.r1 != nullptr;
+    // this thread's two rows of the product are the group's heads g and g + 8
+    float r1v[2] = {0.0f, 0.0f}, r2v[2] = {0.0f, 0.0f};
+    if (has_bias) {
+        if (g < G) { r1v[0] = a.r1[hk * G + g]; r2v[0] = a.r2[hk * G + g]; }
+        if (g + 8 < G) { r1v[1] = a.r1[hk * G + g + 8]; r2v[1] = a.r2[hk * G + g + 8]; }
+    }
+    pdl_wait();
+
+    const uint32_t my_s = (uint32_t)__cvta_generic_to_shared(sd_smem) + (uint32_t)(warp * 2 * TILE_BYTES);
+    auto load_tile = [&](int tile, int buf) {
+        const int key0 = tile * SD_KEYS;
+        const int p_eff = a.ring > 0 ? key0 % a.ring : key0;
+        int page = a.page_table[(size_t)b * a.table_stride + (p_eff >> 6)];
+        if (page < 0) page = 0;                                    // (a tile beyond the end: masked)
+        const long long r0 = ((long long)page * a.n_kv + hk) * MF_PAGE + (key0 & (MF_PAGE - 1));
+        const uint32_t dst = my_s + (uint32_t)(buf * TILE_BYTES);
+        sd_copy_tile<HDP>(dst, a.k + r0 * hd, hd, lane);
+        sd_copy_tile<VDP>(dst + SD_KEYS * HDP * 2, a.v + r0 * vd, vd, lane);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    int tile = tile_lo + warp;
+    if (tile <= tile_hi) load_tile(tile, 0);
+
+    float m_r[2] = {-INFINITY, -INFINITY}, l_r[2] = {0.0f, 0.0f};
+    float o[VDP / 8][4];
+#pragma unroll
+    for (int i = 0; i < VDP / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
+    uint32_t qa[HDP / 16][4];
+    {
+        const __nv_bfloat16* q_lo = a.q + ((long long)row * a.n_heads + hk * G + g) * hd + 2 * t;
+        const __nv_bfloat16* q_hi = q_lo + 8 * (long long)hd;
+        const bool lo_ok = g < G, hi_ok = g + 8 < G;
+#pragma unroll
+        for (int ks = 0; ks < HDP / 16; ++ks) {
+            const bool c0 = 16 * ks + 2 * t < hd, c1 = 16 * ks + 8 + 2 * t < hd;
+            qa[ks][0] = lo_ok && c0 ? *reinterpret_cast<const uint32_t*>(q_lo + 16 * ks) : 0u;
+            qa[ks][1] = hi_ok && c0 ? *reinterpret_cast<const uint32_t*>(q_hi + 16 * ks) : 0u;
+            qa[ks][2] = lo_ok && c1 ? *reinterpret_cast<const uint32_t*>(q_lo + 16 * ks + 8) : 0u;
+            qa[ks][3] = hi_ok && c1 ? *reinterpret_cast<const uint32_t*>(q_hi + 16 * ks + 8) : 0u;
+        }
+    }
+    const uint32_t k_lane = (uint32_t)((((lane >> 4) * 8 + (lane & 7)) * CPRK) * 16);
+    const uint32_t v_lane = (uint32_t)(((((lane >> 3) & 1) * 8 + (lane & 7)) * CPRV) * 16);
+    uint32_t k_col[HDP / 16], v_col[VDP / 16];
+#pragma unroll
+    for (int i = 0; i < HDP / 16; ++i) k_col[i] = (uint32_t)(((2 * i + ((lane >> 3) & 1)) ^ (lane & 7)) * 16);
+#pragma unroll
+    for (int i = 0; i < VDP / 16; ++i) v_col[i] = (uint32_t)(((2 * i + (lane >> 4)) ^ (lane & 7)) * 16);
+
+    for (int it = 0; tile <= tile_hi; tile += SD_WARPS, ++it) {
+        const int buf = it & 1;
+        if (tile + SD_WARPS <= tile_hi) {
+            load_tile(tile + SD_WARPS, buf ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncwarp();
+        // S[16][32] = Q K^T
+        float s[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f; }
+        const uint32_t ks_base = my_s + (uint32_t)(buf * TILE_BYTES) + k_lane;
+#pragma unroll
+        for (int ks = 0; ks < HDP / 16; ++ks) {
+#pragma unroll
+            for (int np = 0; np < 2; ++np) {
+                uint32_t b0, b1, b2, b3;
+                sm_ldsm_x4(ks_base + k_col[ks] + (uint32_t)(np * 16 * CPRK * 16), b0, b1, b2, b3);
+                sm_mma16816(s[2 * np], qa[ks], b0, b1);
+                sm_mma16816(s[2 * np + 1], qa[ks], b2, b3);
+            }
+        }
+        const int key0 = tile * SD_KEYS;
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = key0 + nt * 8 + 2 * t + (e & 1);
+                const int d = pos - key;
+                const bool vis = d >= 0 && key >= lo;
+                float x = s[nt][e] * a.scale_log2;
+                if (has_bias && vis) x -= r1v[e >> 1] * __log2f(fmaf(r2v[e >> 1], (float)d, 1.0f));
+                s[nt][e] = vis ? x : -INFINITY;
+            }
+        }
+        float m_new[2] = {m_r[0], m_r[1]};
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            m_new[0] = fmaxf(m_new[0], fmaxf(s[nt][0], s[nt][1]));
+            m_new[1] = fmaxf(m_new[1], fmaxf(s[nt][2], s[nt][3]));
+        }
+        float corr[2], m_use[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            m_new[r] = fmaxf(m_new[r], __shfl_xor_sync(0xffffffffu, m_new[r], 1));
+            m_new[r] = fmaxf(m_new[r], __shfl_xor_sync(0xffffffffu, m_new[r], 2));
+            m_use[r] = m_new[r] == -INFINITY ? 0.0f : m_new[r];
+            corr[r] = m_r[r] == -INFINITY ? 0.0f : exp2f(m_r[r] - m_use[r]);
+            m_r[r] = m_new[r];
+            l_r[r] *= corr[r];
+        }
+#pragma unroll
+        for (int i = 0; i < VDP / 8; ++i) {
+            o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1];
+        }
+        uint32_t pa[2][4];
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            float p[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                p[e] = exp2f(s[nt][e] - m_use[e >> 1]);
+                l_r[e >> 1] += p[e];
+            }
+            pa[nt >> 1][(nt & 1) * 2 + 0] = sm_pack2(p[0], p[1]);
+            pa[nt >> 1][(nt & 1) * 2 + 1] = sm_pack2(p[2], p[3]);
+        }
+        const uint32_t vs_base = my_s + (uint32_t)(buf * TILE_BYTES + SD_KEYS * HDP * 2) + v_lane;
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks) {
+#pragma unroll
+            for (int np = 0; np < VDP / 16; ++np) {
+                uint32_t x0, x1, x2, x3;
+                sm_ldsm_x4_trans(vs_base + v_col[np] + (uint32_t)(ks * 16 * CPRV * 16), x0, x1, x2, x3);
+                sm_mma16816(o[2 * np], pa[ks], x0, x1);
+                sm_mma16816(o[2 * np + 1], pa[ks], x2, x3);
+            }
+        }
+        __syncwarp();                                             // the buffer may be refilled now
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l_r[r] += __shfl_xor_sync(0xffffffffu, l_r[r], 1);
+        l_r[r] += __shfl_xor_sync(0xffffffffu, l_r[r], 2);
+    }
+    // ---- the four warps' results, merged in warp order ------------------------------------------
+    __syncthreads();                                              // every warp is done with its tiles
+    float* o_s = (float*)sd_smem;                                 // [SD_WARPS][16][OS]
+    float* ml_s = o_s + SD_WARPS * 16 * OS;                       // [SD_WARPS][16][2]
+#pragma unroll
+    for (int nt = 0; nt < VDP / 8; ++nt) {
+        float* p0 = o_s + ((size_t)warp * 16 + g) * OS + nt * 8 + 2 * t;
+        p0[0] = o[nt][0]; p0[1] = o[nt][1];
+        p0[8 * OS] = o[nt][2]; p0[8 * OS + 1] = o[nt][3];
+    }
+    if (t == 0) {
+        ml_s[(warp * 16 + g) * 2] = m_r[0];     ml_s[(warp * 16 + g) * 2 + 1] = l_r[0];
+        ml_s[(warp * 16 + g + 8) * 2] = m_r[1]; ml_s[(warp * 16 + g + 8) * 2 + 1] = l_r[1];
+    }
+    __syncthreads();
+    for (int idx = tid; idx < G * VDP; idx += SD_WARPS * 32) {
+        const int r = idx / VDP, d = idx - r * VDP;
+        if (d >= vd) continue;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < SD_WARPS; ++w) m = fmaxf(m, ml_s[(w * 16 + r) * 2]);
+        float l = 0.0f, acc = 0.0f;
+#pragma unroll
+        for (int w = 0; w < SD_WARPS; ++w) {
+            const float mw = ml_s[(w * 16 + r) * 2];
+            if (mw > -INFINITY) {
+                const float f = exp2f(mw - m);
+                l = fmaf(ml_s[(w * 16 + r) * 2 + 1], f, l);
+                acc = fmaf(o_s[((size_t)w * 16 + r) * OS + d], f, acc);
+            }
+        }
+        const int head = hk * G + r;
+        if (a.n_splits > 1) {
+            float* part = a.partial + (((size_t)row * a.n_heads + head) * a.n_splits + split) * (vd + 2);
+            if (d == 0) { part[0] = m; part[1] = l; }
+            part[2 + d] = acc;
+        } else {
+            float mf = m;
+            if (a.sink) {                                         // the sink: a key of score 0, no value
+                mf = fmaxf(m, 0.0f);
+                const float f = m > -INFINITY ? exp2f(m - mf) : 0.0f;
+                l = l * f + exp2f(-mf);
+                acc *= f;
+            }
+            a.out[((size_t)row * a.n_heads + head) * vd + d] = __float2bfloat16_rn(acc / l);
+        }
+    }
+}
+
+// merges the splits of one (query, head) in split order and adds the sink
+__global__ void sink_decode_combine_kernel(const float* __restrict__ partial,
+                                           __nv_bfloat16* __restrict__ out, int n_splits, int vd,
+                                           int sink) {
+    pdl_prologue();
+    const size_t rh = blockIdx.x;
+    const size_t stride = (size_t)(vd + 2);
+    const float* p = partial + rh * n_splits * stride;
+    float m = sink ? 0.0f : -INFINITY;
+    for (int c = 0; c < n_splits; ++c) m = fmaxf(m, p[c * stride]);
+    float l = sink ? exp2f(-m) : 0.0f;
+    for (int c = 0; c < n_splits; ++c) {
+        const float mc = p[c * stride];
+        if (mc > -INFINITY) l = fmaf(p[c * stride + 1], exp2f(mc - m), l);
+    }
+    const float inv = 1.0f / l;
+    for (int d = threadIdx.x; d < vd; d += blockDim.x) {
+        float acc = 0.0f;
+        for (int c = 0; c < n_splits; ++c) {
+            const float mc = p[c * stride];
+            if (mc > -INFINITY) acc = fmaf(p[c * stride + 2 + d], exp2f(mc - m), acc);
+        }
+        out[rh * vd + d] = __float2bfloat16_rn(acc * inv);
+    }
+}
+
+// How the keys of single queries are cut: (tiles of 32 keys per CTA, splits), from the sizes
+// only.  `reach_keys`: the most keys a query sees (its reach, or the longest sequence).
+extern "C" int mf_sink_decode_plan(int rows, int n_kv, int reach_keys, int* tiles_per_cta,
+                                   int* n_splits) {
+    const int n_tiles = reach_keys / SD_KEYS + 2;                  // the range need not start on a tile
+    int splits = (2 * mf_sm_count() + rows * n_kv - 1) / (rows * n_kv > 0 ? rows * n_kv : 1);
+    const int most = (n_tiles + SD_WARPS - 1) / SD_WARPS;
+    if (splits > most) splits = most;
+    if (splits < 1) splits = 1;
+    int tpc = (n_tiles + splits - 1) / splits;
+    tpc = ((tpc + SD_WARPS - 1) / SD_WARPS) * SD_WARPS;
+    *tiles_per_cta = tpc;
+    *n_splits = (n_tiles + tpc - 1) / tpc;
+    return 0;
+}
+
+template <int HDP, int VDP>
+static int launch_sink_decode(const SinkDecodeArgs& a, int rows, cudaStream_t stream) {
+    constexpr int tiles = SD_WARPS * 2 * SD_KEYS * (HDP + VDP) * 2;
+    constexpr int merge = SD_WARPS * 16 * (VDP + 4) * 4 + SD_WARPS * 16 * 2 * 4;
+    constexpr int smem = tiles > merge ? tiles : merge;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(sink_attention_decode_kernel<HDP, VDP>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    mf_launch(sink_attention_decode_kernel<HDP, VDP>, dim3(a.n_splits, a.n_kv, rows),
+              dim3(SD_WARPS * 32), (size_t)smem, stream, a);
+    return MF_LAUNCH_CHECK();
+}
+
+// Every row of q [rows][n_heads][hd] (bfloat16) is a query at row_pos over the paged cache.
+// `reach_keys`: the most keys a query sees (chunk, window, or the longest sequence's length).
+// `partial`: float32 scratch of rows * n_heads * splits * (vd + 2) floats when the plan has
+// more than one split (mf_sink_decode_plan), else unused.
+extern "C" int mf_sink_attention_decode(const void* q, const void* k_cache, const void* v_cache,
+                                        const int* row_seq, const int* row_pos,
+                                        const int* page_table, int table_stride, int ring,
+                                        void* out, float* partial, const float* r1,
+                                        const float* r2, int rows, int n_heads, int n_kv, int hd,
+                                        int vd, int window, int chunk, int sink, float scale,
+                                        int reach_keys, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (!mf_sink_attention_mma_supported(hd, vd) || n_kv <= 0 || n_heads % n_kv != 0) return MF_ERR_UNSUPPORTED;
+    if (n_heads / n_kv > 16 || n_kv > 65535 || rows > 65535) return MF_ERR_UNSUPPORTED;
+    if (page_table == nullptr || window < 0 || chunk < 0) return MF_ERR_ARGUMENT;
+    SinkDecodeArgs a;
+    a.q = (const __nv_bfloat16*)q; a.k = (const __nv_bfloat16*)k_cache;
+    a.v = (const __nv_bfloat16*)v_cache; a.row_seq = row_seq; a.row_pos = row_pos;
+    a.page_table = page_table; a.table_stride = table_stride; a.ring = ring;
+    a.out = (__nv_bfloat16*)out; a.partial = partial; a.r1 = r1; a.r2 = r2;
+    a.n_heads = n_heads; a.n_kv = n_kv; a.hd = hd; a.vd = vd; a.window = window; a.chunk = chunk;
+    a.sink = sink ? 1 : 0;
+    a.scale_log2 = scale * 1.4426950408889634f;
+    mf_sink_decode_plan(rows, n_kv, reach_keys, &a.tiles_per_cta, &a.n_splits);
+    if (a.n_splits > 1 && partial == nullptr) return MF_ERR_ARGUMENT;
+    int e;
+    if (hd <= 64) e = vd <= 64 ? launch_sink_decode<64, 64>(a, rows, stream)
+                               : launch_sink_decode<64, 128>(a, rows, stream);
+    else e = vd <= 64 ? launch_sink_decode<128, 64>(a, rows, stream)
+                      : launch_sink_decode<128, 128>(a, rows, stream);
+    if (e || a.n_splits == 1) return e;
+    mf_launch_ex(false, sink_decode_combine_kernel, dim3(rows * n_heads), dim3(vd <= 64 ? 64 : 128), 0,
+                 stream, (const float*)partial, (__nv_bfloat16*)out, a.n_splits, vd, a.sink);
+    return MF_LAUNCH_CHECK();
+}

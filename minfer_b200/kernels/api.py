@@ -138,6 +138,11 @@ def _sig_attention_sink(lib: ctypes.CDLL) -> None:
                                           [c_int] * 9 + [c_float, c_void_p])
 
 
+    lib.mf_sink_decode_plan.argtypes = [c_int, c_int, c_int, c_void_p, c_void_p]
+    lib.mf_sink_attention_decode.argtypes = ([c_void_p] * 6 + [c_int, c_int] + [c_void_p] * 4 +
+                                             [c_int] * 8 + [c_float, c_int, c_void_p])
+
+
 def _sig_sampling(lib: ctypes.CDLL) -> None:
     lib.mf_sample.argtypes = [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p,
                               c_void_p, c_float, c_int, c_float, c_float, c_float, c_float,
@@ -807,6 +812,49 @@ def sink_attention_mma(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seq
         _ptr(out, "out"), _f32(r1, "r1"), _f32(r2, "r2"), int(n_rows), int(max_row_tokens), n_heads,
         n_kv, head_dim, value_dim, int(window), int(chunk), 1 if sink else 0, float(scale),
         _stream()), "sink_attention_mma")
+
+
+_SINK_PLANS: dict = {}
+
+
+def sink_decode_plan(rows: int, n_kv: int, reach_keys: int) -> tuple[int, int]:
+    """(tiles of 32 keys per CTA, key splits) of the kernel for single queries."""
+    key = (rows, n_kv, reach_keys)
+    got = _SINK_PLANS.get(key)
+    if got is None:
+        tpc, sp = ctypes.c_int(0), ctypes.c_int(0)
+        _lib("attention_sink").mf_sink_decode_plan(rows, n_kv, reach_keys, ctypes.addressof(tpc),
+                                                   ctypes.addressof(sp))
+        got = (tpc.value, sp.value)
+        _SINK_PLANS[key] = got
+    return got
+
+
+def sink_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                          row_seq: torch.Tensor, row_pos: torch.Tensor, page_table: torch.Tensor,
+                          table_stride: int, ring: int, out: torch.Tensor,
+                          r1: Optional[torch.Tensor], r2: Optional[torch.Tensor], n_heads: int,
+                          n_kv: int, head_dim: int, value_dim: int, window: int, chunk: int,
+                          sink: bool, scale: float, reach_keys: int) -> None:
+    """Every row of ``q`` a query at its own position over the paged cache, on tensor cores
+    (bfloat16, up to 16 query heads per key/value head).  ``reach_keys``: the most keys a query
+    sees (its chunk or window, or the longest sequence's length)."""
+    rows = q.shape[0]
+    if q.dtype != torch.bfloat16 or out.shape != (rows, n_heads * value_dim):
+        raise KernelError("sink_attention_decode: bfloat16 only, out [rows, heads * value size]")
+    if (r1 is None) != (r2 is None):
+        raise KernelError("sink_attention_decode: inconsistent arguments")
+    _, splits = sink_decode_plan(rows, n_kv, int(reach_keys))
+    partial = None
+    if splits > 1:
+        partial = torch.empty(rows * n_heads * splits * (value_dim + 2), dtype=torch.float32,
+                              device=q.device)
+    _check(_lib("attention_sink").mf_sink_attention_decode(
+        _ptr(q, "q"), _ptr(k_cache, "k_cache"), _ptr(v_cache, "v_cache"), _i32(row_seq, "row_seq"),
+        _i32(row_pos, "row_pos"), _i32(page_table, "page_table"), int(table_stride), int(ring),
+        _ptr(out, "out"), _f32(partial, "partial"), _f32(r1, "r1"), _f32(r2, "r2"), rows, n_heads,
+        n_kv, head_dim, value_dim, int(window), int(chunk), 1 if sink else 0, float(scale),
+        int(reach_keys), _stream()), "sink_attention_decode", 2 if splits > 1 else 1)
 
 
 def sampler_state_ints() -> int:

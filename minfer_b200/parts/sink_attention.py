@@ -182,6 +182,14 @@ class SinkAttention(Mixer):
                                      self.window, self.chunk, self.sink, self.scale)
                 self._project_out(o, ctx, residual)
                 return
+            if tensor_cores and nh // nk <= 16:
+                # single queries: the heads of a key/value head are the rows of the product
+                K.sink_attention_decode(q, cache.k, cache.v, ctx.token_row, ctx.positions,
+                                        cache.page_table, cache.table_stride, cache.ring, o,
+                                        self.r1, self.r2, nh, nk, hd, vd, self.window, self.chunk,
+                                        self.sink, self.scale, reach if reach > 0 else ctx.max_end)
+                self._project_out(o, ctx, residual)
+                return
             K.sink_attention_paged(q, cache.k, cache.v, ctx.token_row, ctx.positions,
                                    cache.page_table, cache.table_stride, cache.ring, o, self.r1,
                                    self.r2, nh, nk, hd, vd, self.window, self.chunk, self.sink,

@@ -364,3 +364,48 @@ def test_xielu_in_the_products_epilogue():
             want = P.xielu(x.double().cpu() @ w.double().cpu().T, a)
             assert _err(out, want) < (1.2e-2 if out_dtype == torch.bfloat16 else 2e-4)
     assert int(status.item()) == 0
+
+
+@pytest.mark.parametrize("case", MMA_CASES)
+@pytest.mark.parametrize("ringed", [False, True])
+@pytest.mark.parametrize("sink", [True, False])
+def test_single_query_kernel_on_tensor_cores(case, ringed, sink):
+    """The last positions of every sequence, each a query of its own, over the paged cache."""
+    heads, kv, hd, vd, chunk, lengths = case
+    if ringed and (chunk == 0 or chunk > 1000):
+        pytest.skip("a ring needs a bound on how far a query looks back")
+    if heads // kv > 16:
+        pytest.skip("more query heads per key/value head than the product has rows")
+    q, k, v, r1, r2 = _qkv_case(7 * hd + vd, heads, kv, hd, vd, lengths)
+    _spike(q, k, v, lengths, chunk, heads // kv)
+    t = torch.bfloat16
+    qd, kd, vd_ = q.to(t), k.to(t), v.to(t)
+    want_all = _plain_rows(qd.double(), kd.double(), vd_.double(), r1, r2, 0.3, chunk, lengths)
+    if not sink:
+        ones = _plain_rows(qd.double(), kd.double(), torch.ones_like(vd_).double(), r1, r2, 0.3, chunk, lengths)
+        want_all = (want_all.view(-1, heads, vd) / ones.view(-1, heads, vd)[..., :1]).reshape(want_all.shape)
+    ring = -(-(chunk + 20) // 64) * 64 if ringed else 0
+    kc, vc, table, stride = _paged(kd, vd_, lengths, ring, seed=hd + 1)
+    rows, row_seq, row_pos, at = [], [], [], 0
+    for b, n in enumerate(lengths):
+        tail = min(n, 21 if ring else 40)
+        for p in list(range(n - tail, n)) + ([0] if not ring else []):
+            rows.append(at + p)
+            row_seq.append(b)
+            row_pos.append(p)
+        at += n
+    out = torch.empty(len(rows), heads * vd, dtype=t, device=DEV)
+    reach = chunk if chunk > 0 else max(lengths)
+    K().sink_attention_decode(qd[rows].contiguous().to(DEV), kc.to(DEV), vc.to(DEV), _i32(row_seq),
+                              _i32(row_pos), table.reshape(-1).to(DEV), stride, ring, out,
+                              r1.float().to(DEV), r2.float().to(DEV), heads, kv, hd, vd, 0, chunk, sink,
+                              0.3, reach)
+    assert _err(out, want_all[rows]) < 2e-2
+    # one query alone: the plan cuts its keys into many splits, which the merge kernel adds up
+    one = [len(rows) - 1]
+    out1 = torch.empty(1, heads * vd, dtype=t, device=DEV)
+    K().sink_attention_decode(qd[rows][one].contiguous().to(DEV), kc.to(DEV), vc.to(DEV),
+                              _i32([row_seq[-1]]), _i32([row_pos[-1]]), table.reshape(-1).to(DEV),
+                              stride, ring, out1, r1.float().to(DEV), r2.float().to(DEV), heads, kv, hd,
+                              vd, 0, chunk, sink, 0.3, reach)
+    assert _err(out1, want_all[[rows[-1]]]) < 2e-2

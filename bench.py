@@ -149,7 +149,10 @@ def decode_bytes(model, batch, context_tokens):
     for call in plan.schedule:
         req = model.blocks[call.layer].mixer.cache_request()
         if req is not None and call.writes_cache:
-            kv += 2 * req.n_kv_heads * req.head_dim * esz * context_tokens
+            # keys and values may differ in width; a layer with a window or a chunk mask reads
+            # at most that many positions back
+            seen = min(context_tokens, req.window) if req.window else context_tokens
+            kv += req.n_kv_heads * (req.head_dim + (req.value_dim or req.head_dim)) * esz * seen
     return weights + batch * kv
 
 
@@ -323,6 +326,181 @@ def point_long(engine, torch, K, pk, cfg, context=32000, steps=32):
                  "decode_7b_b1_ctx32000": (time_decode.window, ms_step)}
 
 
+# ------------------------------------------------------------------------------------------
+# --workload furitar: the Furitar design beside the Qwen2 decoder at equal sizes
+# ------------------------------------------------------------------------------------------
+def furitar_config(width, heads, kv, dim, vdim, ff, chunk, layers, vocab, positions):
+    layer = {"type": "attention",
+             "mixer": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim,
+                       "scale": dim ** -0.5 * 8.0, "mask": {"size": chunk}},
+             "mlp": {"kind": "dense", "ff": ff}}
+    return {"architecture": "Furitar", "vocab": vocab, "width": width, "max_positions": positions,
+            "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5}, "logit_scale": 1.0,
+            "layers": [layer] * layers}
+
+
+# (name, width, heads, kv heads, head size, Qwen2's intermediate size, chunk, layers): the dense
+# feed-forward gets 1.5 x the gated one's inner width, so both have the same weights per layer
+FURITAR_SIZES = [("w2048", 2048, 16, 4, 128, 5632, 1024, 8),
+                 ("w4096", 4096, 32, 8, 128, 11264, 2048, 6)]
+FURITAR_VOCAB = 32000
+
+
+def furitar_prefill_flops(cfg, tokens):
+    """Matrix-product flops of one whole prompt (head on the last row only) plus the attention
+    of the keys a chunk mask leaves visible."""
+    w, flops = cfg["width"], 0.0
+    for layer in cfg["layers"]:
+        m = layer["mixer"]
+        per_token = 2 * w * ((m["heads"] + m["kv_heads"]) * m["dim"] + m["kv_heads"] * m["vdim"])
+        per_token += 2 * w * m["heads"] * m["vdim"]
+        if layer["mlp"] is not None:
+            per_token += 4 * w * layer["mlp"]["ff"]
+        flops += per_token * tokens
+        c = m["mask"]["size"]
+        full, rest = divmod(tokens, c)
+        pairs = full * c * (c + 1) / 2 + rest * (rest + 1) / 2
+        flops += m["heads"] * 2 * (m["dim"] + m["vdim"]) * pairs
+    return flops + 2 * w * cfg["vocab"]
+
+
+def _median_ms(torch, fn, reps=20, flush=None):
+    """Median device time of ``fn`` over ``reps`` runs after three warm-ups; L2 is flushed by a
+    write of ``flush`` (a buffer larger than L2) before each."""
+    times = []
+    for i in range(reps + 3):
+        if flush is not None:
+            flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        if i >= 3:
+            times.append(a.elapsed_time(b))
+    return statistics.median(times)
+
+
+def furitar_attention_kernels(torch, K, pk, heads, kv, dim, chunk, tokens=2048, batch=8):
+    """The attention kernels alone at one layer's sizes: a whole prompt of ``tokens`` and
+    ``batch`` single queries at position ``tokens`` - 1, Furitar's beside Qwen2's, each with its
+    share of its roofline (flops of the visible pairs over the measured product peak for a
+    prompt; bytes of the visible keys and values over the measured copy bandwidth for single
+    queries)."""
+    from minfer_b200.parts.attention import decode_chunks
+    dev, bf = "cuda:0", torch.bfloat16
+    g = torch.Generator(device=dev).manual_seed(0)
+    rnd = lambda *shape: torch.randn(*shape, generator=g, device=dev, dtype=torch.float32).to(bf)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    out = {}
+    # a whole prompt
+    q, k, v = rnd(tokens, heads, dim), rnd(tokens, kv, dim), rnd(tokens, kv, dim)
+    o = torch.empty(tokens, heads * dim, dtype=bf, device=dev)
+    cu = torch.tensor([0, tokens], dtype=torch.int32, device=dev)
+    r1 = torch.full((heads,), 0.5, dtype=torch.float32, device=dev)
+    r2 = torch.full((heads,), 0.5, dtype=torch.float32, device=dev)
+    scale = dim ** -0.5
+    ms_f = _median_ms(torch, lambda: K.sink_attention_mma(q, k, v, cu, None, None, 0, 0, o, r1, r2, 1,
+                                                          tokens, heads, kv, dim, dim, 0, chunk, True,
+                                                          scale), flush=flush)
+    ms_q = _median_ms(torch, lambda: K.attention_prefill_tc(q, k, v, cu, o, 1, tokens, heads, kv, dim, 0,
+                                                            scale, status), flush=flush)
+    full, rest = divmod(tokens, chunk)
+    pairs_f = full * chunk * (chunk + 1) / 2 + rest * (rest + 1) / 2
+    pairs_q = tokens * (tokens + 1) / 2
+    peak = pk["bf16_tflops"] * 1e12
+    out["prompt"] = {
+        "furitar_us": round(ms_f * 1e3, 1), "qwen2_us": round(ms_q * 1e3, 1),
+        "furitar_frac": round(heads * 4 * dim * pairs_f / (ms_f * 1e-3) / peak, 4),
+        "qwen2_frac": round(heads * 4 * dim * pairs_q / (ms_q * 1e-3) / peak, 4)}
+    # single queries over pages
+    pages_per = tokens // 64
+    n_pages = batch * pages_per
+    kc, vc = rnd(n_pages, kv, 64, dim), rnd(n_pages, kv, 64, dim)
+    table = torch.arange(n_pages, dtype=torch.int32, device=dev)
+    rows = torch.arange(batch, dtype=torch.int32, device=dev)
+    pos = torch.full((batch,), tokens - 1, dtype=torch.int32, device=dev)
+    q1 = rnd(batch, heads, dim)
+    o1 = torch.empty(batch, heads * dim, dtype=bf, device=dev)
+    ms_f = _median_ms(torch, lambda: K.sink_attention_decode(q1, kc, vc, rows, pos, table, pages_per, 0,
+                                                             o1, r1, r2, heads, kv, dim, dim, 0, chunk,
+                                                             True, scale, chunk), flush=flush)
+    ck, n_ck = decode_chunks(batch * kv, tokens)
+    part = torch.empty(batch * heads * n_ck * (dim + 2), dtype=torch.float32, device=dev)
+    ms_q = _median_ms(torch, lambda: K.attention_paged(q1, kc, vc, rows, pos, table, pages_per, 0, o1,
+                                                       part, heads, kv, dim, 0, ck, n_ck, scale,
+                                                       status=status, old_keys_final=True), flush=flush)
+    seen_f = min(chunk, (tokens - 1) % chunk + 1)
+    bw = pk["hbm_gbs"] * 1e9
+    out["single"] = {
+        "furitar_us": round(ms_f * 1e3, 1), "qwen2_us": round(ms_q * 1e3, 1),
+        "furitar_keys": seen_f, "qwen2_keys": tokens,
+        "furitar_frac": round(batch * kv * seen_f * 2 * dim * 2 / (ms_f * 1e-3) / bw, 4),
+        "qwen2_frac": round(batch * kv * tokens * 2 * dim * 2 / (ms_q * 1e-3) / bw, 4)}
+    return out
+
+
+def workload_furitar(args) -> int:
+    """Prefill of one 2,048-token prompt and decoding at batch 8 from 2,048-token contexts, for
+    the Furitar design and for the Qwen2 decoder at equal width, heads, head size, layers and
+    feed-forward weights, random weights, bfloat16; and the attention kernels of both alone."""
+    import torch
+    from minfer_b200.engine.generate import Generator
+    from minfer_b200.kernels import api as K
+    from minfer_b200.model import Model
+    pk, pk_kind = peaks()
+    torch.cuda.set_device(0)
+    steps = max(8, min(args.steps, 128))
+    clocks = ClockSampler()
+    clocks.start()
+    t_all = time.time()
+    sizes = []
+    for name, width, heads, kv, dim, inter, chunk, layers in FURITAR_SIZES:
+        cfg_f = furitar_config(width, heads, kv, dim, dim, inter * 3 // 2, chunk, layers,
+                               FURITAR_VOCAB, CONTEXT)
+        cfg_q = dict(CONFIG_7B, vocab_size=FURITAR_VOCAB, hidden_size=width, num_hidden_layers=layers,
+                     num_attention_heads=heads, num_key_value_heads=kv, intermediate_size=inter,
+                     max_position_embeddings=CONTEXT)
+        entry = {"name": name, "width": width, "heads": heads, "kv_heads": kv, "head_size": dim,
+                 "layers": layers, "chunk": chunk, "furitar_ff": inter * 3 // 2, "qwen2_intermediate": inter}
+        for label, cfg in (("furitar", cfg_f), ("qwen2", cfg_q)):
+            model = Model.from_config(cfg, seed=0, dtype="bfloat16", device="cuda:0", make_on="device")
+            gen = Generator(model, max_tokens=BATCH * CONTEXT, max_batch=BATCH)
+            engine = gen.engine
+            g = torch.Generator().manual_seed(2)
+            ids = torch.randint(0, FURITAR_VOCAB, (PROMPT,), generator=g).tolist()
+            ms_prefill = time_prefill(engine, torch, ids, 10)
+            flops = furitar_prefill_flops(cfg, PROMPT) if label == "furitar" else prefill_flops(cfg, PROMPT)
+            ms_step, launched = time_decode(engine, torch, K, BATCH, steps, max(3, args.warmup), PROMPT)
+            ms_med = time_decode.median_ms
+            step_bytes = decode_bytes(model, BATCH, PROMPT + 3 + steps / 2)
+            entry[label] = {
+                "weights_gb": round(model.parameter_bytes() / 1e9, 3),
+                "prefill_tokens_per_s": round(PROMPT * 1e3 / ms_prefill, 1),
+                "prefill_ms": round(ms_prefill, 3),
+                "prefill_frac": round(flops / (ms_prefill * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+                "decode_tokens_per_s": round(BATCH * 1e3 / ms_med, 1),
+                "decode_ms_per_step": round(ms_med, 4), "decode_frac": _frac(step_bytes, ms_med, pk),
+                "decode_launches_per_step": round(launched / steps, 1)}
+            del gen, engine, model
+            torch.cuda.empty_cache()
+        entry["attention_kernels"] = furitar_attention_kernels(torch, K, pk, heads, kv, dim, chunk)
+        sizes.append(entry)
+    summary = clocks.summary((t_all, time.time()))
+    clocks.stop()
+    print(json.dumps({
+        "workload": "furitar", "impl": "ours", "dtype": "bf16", "data": "synthetic", "n_gpus": 1,
+        "metric": "prefill tokens/s of one 2048-token prompt and decode tokens/s at batch 8 from "
+                  "2048-token contexts, Furitar beside Qwen2 at equal sizes",
+        "unit": "tokens/s", "steps": steps, "prompt_len": PROMPT, "batch": BATCH,
+        "fractions": f"prefill: flops over the {pk_kind} bf16 product peak; decode: bytes of the "
+                     f"weights and of the visible cache over the {pk_kind} copy bandwidth",
+        "l2": "weights larger than L2 are read every step; kernels alone: L2 flushed before each run",
+        "clocks": summary, "sizes": sizes}))
+    return 0
+
+
 REF_KERNELS = os.path.join(ROOT, "baseline", "_ref", "libref_kernels.so")
 # the reference's checkout, if it sits beside this repository (or where MINFER_REFERENCE_DIR says)
 REF_SOURCE = os.path.join(os.environ.get("MINFER_REFERENCE_DIR",
@@ -477,6 +655,9 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None,
                     help="run fewer layers than the configuration has (both numbers are reported)")
+    ap.add_argument("--workload", default="qwen2-7b", choices=["qwen2-7b", "furitar"],
+                    help="qwen2-7b (the default): the headline figure and its points; furitar: "
+                         "the Furitar design beside Qwen2 at equal sizes, prefill and decode")
     ap.add_argument("--skip-points", action="store_true",
                     help="only the headline figure and its end-to-end twin")
     args = ap.parse_args()
@@ -490,6 +671,9 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+
+    if args.workload == "furitar":
+        return workload_furitar(args)
 
     import torch
     from minfer_b200.engine.generate import Generator

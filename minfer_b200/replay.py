@@ -40,11 +40,13 @@ def main(argv=None) -> int:
         return 2
     os.makedirs(args.out, exist_ok=True)
     model = Model.from_folder(args.model, args.dtype, "cuda:0")
-    # the cache hands out pages of 64 positions: a request may hold up to 63 positions more
-    # than its tokens, so the pool gets a page per slot on top of what the caller counted
+    # --max-tokens counts tokens, the cache hands out pages of 64 positions: a request may hold
+    # up to 63 positions more than its tokens.  The pool therefore gets a page per slot on top of
+    # what the caller counted, and the caller's own bound is kept here, token by token.
     max_seqs = 256
     engine = Engine(model, max_tokens=args.max_tokens + 64 * max_seqs, max_seqs=max_seqs)
     slot_of: Dict[str, int] = {}
+    held: Dict[str, int] = {}
 
     for line in sys.stdin:
         line = line.strip()
@@ -61,6 +63,12 @@ def main(argv=None) -> int:
                     slot_of[rid] = engine.acquire()
                 slots.append(slot_of[rid])
                 tokens.append([int(t) for t in e["tokens"]])
+                held[rid] = held.get(rid, 0) + len(tokens[-1])
+            if sum(held.values()) > args.max_tokens:
+                from .cache.paged import OutOfPages
+                raise OutOfPages(
+                    f"the cache has no free page left: live requests would hold "
+                    f"{sum(held.values())} tokens, --max-tokens is {args.max_tokens}")
                 want.append([int(x) for x in e.get("want", [])])
             logits = engine.step(slots, tokens, want)
             if logits.shape[0] > 0:
@@ -75,6 +83,7 @@ def main(argv=None) -> int:
             rid = str(rid)
             if rid in slot_of:
                 engine.release(slot_of.pop(rid))
+                held.pop(rid, None)
         print(f"done {step}", flush=True)
     return 0
 

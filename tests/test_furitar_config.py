@@ -122,3 +122,20 @@ def test_plain_mechanisms_by_hand():
     zs = torch.tensor([-e, 0.0, e], dtype=torch.float64)
     y = P.xielu(zs, a)
     assert abs(float(y[1])) < 1e-12 and abs(float((y[2] - y[0]) / (2 * e)) - 0.5) < 1e-5
+
+
+def test_command_line_writes_and_describes_a_random_model(tmp_path, capsys):
+    """``random`` writes a folder from a configuration file; ``--info`` reads it back."""
+    import json
+    from minfer_b200 import cli
+    cfg_path = tmp_path / "cfg.json"
+    cfg_path.write_text(json.dumps(FUR_B))
+    folder = tmp_path / "model"
+    assert cli.main(["random", str(cfg_path), str(folder), "--seed", "3"]) == 0
+    capsys.readouterr()
+    assert cli.main(["--info", str(folder)]) == 0
+    text = capsys.readouterr().out
+    assert "architecture: Furitar" in text and "embed" in text
+    cfg, w = P.load_folder(str(folder))
+    assert cfg["architecture"] == "Furitar" and w["l3.mix.v"].shape == (40, 100)
+    assert "l0.norm2" in w and w["pos"].shape == (400, 100)

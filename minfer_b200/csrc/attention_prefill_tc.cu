@@ -62,7 +62,25 @@ struct FaArgs {
     const int* page_table;    // [sequences][table_stride] pages of 64 positions, -1 = none
     int table_stride;
     int ring;                 // 0 = linear, else position p lies at p % ring
+    // MOD only: scores changed before the softmax, and a sink
+    //   s_ij = (q_i . k_j) * scale - r1[h] ln(1 + r2[h] (i - j));  j visible only if
+    //   floor(i / chunk) == floor(j / chunk) (chunk > 0);  a key of score 0 without a value in
+    //   the softmax's sum (sink)
+    int chunk, sink;
+    int tab_n;                // entries of the bias table in shared memory (0: computed per score)
+    const float* r1;          // [n_heads] or null
+    const float* r2;
 };
+
+#define FA_TAB_PAD 256        // zeros on either side of the bias table (indices of masked scores)
+#define FA_TAB_MAX 4096
+
+// first visible key of a query at `pos`
+__device__ __forceinline__ int fa_first_key(int pos, int window, int chunk) {
+    int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    if (chunk > 0) lo = max(lo, (pos / chunk) * chunk);
+    return lo;
+}
 
 // ---- PTX wrappers --------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t fa_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -194,7 +212,7 @@ __device__ __forceinline__ uint32_t fa_pack(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int HD, bool PAGED>
+template <int HD, bool PAGED, bool MOD>
 __global__ void __launch_bounds__(FA_THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const FaArgs a) {
@@ -219,6 +237,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     uint64_t* o_done = bars + 13;                       // [2 query tiles]
     uint32_t* tmem_slot = (uint32_t*)(bars + 15);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    // MOD: the distance bias in units of the raw score, tab[FA_TAB_PAD + d] = r1 log2(1 + r2 d) /
+    // scale_log2 for 0 <= d < tab_n, zeros around it
+    float* tab = (float*)(bars + 32);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int seq = blockIdx.z, head = blockIdx.x;
@@ -237,7 +258,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     for (int t = 0; t < 2; ++t) {
         const int q0t = q0 + t * FA_Q;
         if (q0t < len) {
-            kb[t] = a.window > 0 ? max(0, pos0 + q0t - a.window + 1) / FA_KEYS : 0;
+            kb[t] = MOD ? fa_first_key(pos0 + q0t, a.window, a.chunk) / FA_KEYS
+                        : (a.window > 0 ? max(0, pos0 + q0t - a.window + 1) / FA_KEYS : 0);
             ke[t] = (pos0 + min(q0t + FA_Q, len) - 1) / FA_KEYS + 1;
         } else {
             kb[t] = ke[t] = 0;
@@ -261,6 +283,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    const bool has_bias = MOD && a.r1 != nullptr;
+    const float bias_r1 = has_bias ? a.r1[head] / a.scale_log2 : 0.0f, bias_r2 = has_bias ? a.r2[head] : 0.0f;
+    if (MOD && has_bias && a.tab_n > 0) {
+        for (int i = tid; i < a.tab_n + 2 * FA_TAB_PAD; i += FA_THREADS) {
+            const int d = i - FA_TAB_PAD;
+            tab[i] = (d >= 0 && d < a.tab_n) ? bias_r1 * log2f(fmaf(bias_r2, (float)d, 1.0f)) : 0.0f;
+        }
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -403,7 +433,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const uint32_t s_addr = lane_addr + (uint32_t)(TM_S + t * 128);
         const uint32_t o_addr = lane_addr + (uint32_t)(TM_O + t * 128);
         const int kb_t = t ? kb[1] : kb[0], ke_t = t ? ke[1] : ke[0];
-        float m = -INFINITY, l = 0.0f;
+        // the sink is a key of score 0: it starts the running maximum
+        float m = (MOD && a.sink) ? 0.0f : -INFINITY, l = 0.0f;
+        const int row_lo = MOD ? fa_first_key(qpos, 0, a.chunk) : 0;              // chunk's first key
+        const int warp_lo = MOD ? fa_first_key(wpos + 31, 0, a.chunk) : 0;
         bool ok = true;
         for (int j = kb_t; j < ke_t; ++j) {
             const int c = j - kb_t;
@@ -412,18 +445,35 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (!fa_wait(fa_smem(&s_full[t]), (uint32_t)(c & 1), abort_flag)) { ok = false; break; }
             fa_fence_after();
             const bool need_mask = key0 + FA_KEYS - 1 > wpos || key0 + FA_KEYS > key_end ||
-                                   (a.window > 0 && key0 < wpos + 31 - a.window + 1);
+                                   (a.window > 0 && key0 < wpos + 31 - a.window + 1) ||
+                                   (MOD && key0 < warp_lo);
             // the whole row of S (128 scores) into registers, masked by position where the tile
             // touches the diagonal, the window's edge or the sequence's end
             uint32_t sr[FA_KEYS];
 #pragma unroll
             for (int c0 = 0; c0 < FA_KEYS; c0 += 32) fa_ld32(s_addr + (uint32_t)c0, sr + c0);
             fa_wait_ld();
+            if (MOD && has_bias) {
+                // the distance bias, in units of the raw score (what is masked below may read the
+                // zeros around the table)
+                if (a.tab_n > 0) {
+                    const float* tp = tab + FA_TAB_PAD + (qpos - key0);
+#pragma unroll
+                    for (int i = 0; i < FA_KEYS; ++i) sr[i] = __float_as_uint(__uint_as_float(sr[i]) - tp[-i]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < FA_KEYS; ++i) {
+                        const float d = (float)max(qpos - key0 - i, 0);
+                        sr[i] = __float_as_uint(__uint_as_float(sr[i]) - bias_r1 * __log2f(fmaf(bias_r2, d, 1.0f)));
+                    }
+                }
+            }
             if (need_mask) {
 #pragma unroll
                 for (int i = 0; i < FA_KEYS; ++i) {
                     const int key = key0 + i;
-                    const bool vis = key <= qpos && key < key_end && (a.window == 0 || qpos - key < a.window);
+                    const bool vis = key <= qpos && key < key_end && (a.window == 0 || qpos - key < a.window) &&
+                                     (!MOD || key >= row_lo);
                     if (!vis) sr[i] = 0xff800000u;            // -inf
                 }
             }
@@ -495,6 +545,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         // ---- the result: O / sum -------------------------------------------------------------
         if (ok && ke_t > kb_t && fa_wait(fa_smem(&o_done[t]), 0u, abort_flag)) {
             fa_fence_after();
+            if (MOD && a.sink) l += exp2f(-m * a.scale_log2);         // m >= 0 from the start
             const float inv = 1.0f / l;
             __nv_bfloat16* o = a.out + ((long long)(tok0 + qrow) * a.n_heads + head) * HD;
 #pragma unroll 1
@@ -579,19 +630,19 @@ static int fa_cache_map(CUtensorMap* map, const void* ptr, long long rows, int h
     return r == CUDA_SUCCESS ? 0 : MF_ERR_TENSORMAP;
 }
 
-template <int HD, bool PAGED>
+template <int HD, bool PAGED, bool MOD = false>
 static int fa_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FaArgs& a,
                      int n_seqs, int max_len, cudaStream_t stream) {
-    constexpr int smem = (HD / 64) * 16384 * 6 + 1024 + 256;
+    constexpr int smem = (HD / 64) * 16384 * 6 + 1024 + 256 + (MOD ? (FA_TAB_MAX + 2 * FA_TAB_PAD) * 4 : 0);
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD, PAGED>,
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD, PAGED, MOD>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     dim3 grid(a.n_heads, (max_len + FA_CTA_Q - 1) / FA_CTA_Q, n_seqs);
-    mf_launch(attention_prefill_tc_kernel<HD, PAGED>, grid, dim3(FA_THREADS), smem, stream, mq, mk, mv, a);
+    mf_launch(attention_prefill_tc_kernel<HD, PAGED, MOD>, grid, dim3(FA_THREADS), smem, stream, mq, mk, mv, a);
     return MF_LAUNCH_CHECK();
 }
 
@@ -645,4 +696,47 @@ extern "C" int mf_attention_prefill_tc_paged(const void* q, const void* k_cache,
     a.seq_end = seq_end; a.page_table = page_table; a.table_stride = table_stride; a.ring = ring;
     return hd == 64 ? fa_launch<64, true>(mq, mk, mv, a, n_seqs, max_len, stream)
                     : fa_launch<128, true>(mq, mk, mv, a, n_seqs, max_len, stream);
+}
+
+// The same kernel with the scores changed before the softmax and a sink (MOD, see FaArgs):
+// distance bias r1 ln(1 + r2 (i - j)) per head (r1 null: none), chunk mask, sink.  `page_table`
+// null: k, v are the step's packed rows and every sequence starts at position 0; else they are
+// the paged cache [cache_pages][n_kv][64][hd] and sequence b ends at seq_end[b] after the step.
+extern "C" int mf_sink_attention_tc(const void* q, const void* k, const void* v, const int* cu_seqlens,
+                                    const int* seq_end, const int* page_table, int table_stride, int ring,
+                                    void* out, const float* r1, const float* r2, int n_tokens, int n_seqs,
+                                    int max_len, int n_heads, int n_kv, int hd, int window, int chunk,
+                                    int sink, float scale, long long cache_pages, unsigned* status,
+                                    cudaStream_t stream) {
+    if (n_seqs <= 0 || max_len <= 0 || n_tokens <= 0) return 0;
+    if ((hd != 64 && hd != 128) || n_kv <= 0 || n_heads % n_kv != 0) return MF_ERR_UNSUPPORTED;
+    if (n_seqs > 65535 || (max_len + FA_CTA_Q - 1) / FA_CTA_Q > 65535) return MF_ERR_UNSUPPORTED;
+    if (((uintptr_t)q & 15) || ((uintptr_t)k & 15) || ((uintptr_t)v & 15) || ((uintptr_t)out & 15))
+        return MF_ERR_UNSUPPORTED;
+    if (window < 0 || chunk < 0 || (r1 == nullptr) != (r2 == nullptr) || !(scale > 0.0f)) return MF_ERR_ARGUMENT;
+    const bool paged = page_table != nullptr;
+    if (paged && (cache_pages <= 0 || table_stride <= 0 || ring % MF_PAGE != 0 || !seq_end)) return MF_ERR_ARGUMENT;
+    CUtensorMap mq, mk, mv;
+    if (int e = fa_map(&mq, q, n_tokens, (long long)n_heads * hd)) return e;
+    if (paged) {
+        if (int e = fa_cache_map(&mk, k, cache_pages * n_kv * MF_PAGE, hd)) return e;
+        if (int e = fa_cache_map(&mv, v, cache_pages * n_kv * MF_PAGE, hd)) return e;
+    } else {
+        if (int e = fa_map(&mk, k, n_tokens, (long long)n_kv * hd)) return e;
+        if (int e = fa_map(&mv, v, n_tokens, (long long)n_kv * hd)) return e;
+    }
+    FaArgs a{};
+    a.cu_seqlens = cu_seqlens; a.out = (__nv_bfloat16*)out; a.status = status;
+    a.n_heads = n_heads; a.n_kv = n_kv; a.window = window;
+    a.scale_log2 = scale * 1.4426950408889634f;
+    a.seq_end = seq_end; a.page_table = page_table; a.table_stride = table_stride; a.ring = ring;
+    a.chunk = chunk; a.sink = sink ? 1 : 0; a.r1 = r1; a.r2 = r2;
+    int reach = chunk;
+    if (window > 0 && (reach == 0 || window < reach)) reach = window;
+    a.tab_n = (r1 != nullptr && reach > 0 && reach <= FA_TAB_MAX) ? reach : 0;
+    if (paged)
+        return hd == 64 ? fa_launch<64, true, true>(mq, mk, mv, a, n_seqs, max_len, stream)
+                        : fa_launch<128, true, true>(mq, mk, mv, a, n_seqs, max_len, stream);
+    return hd == 64 ? fa_launch<64, false, true>(mq, mk, mv, a, n_seqs, max_len, stream)
+                    : fa_launch<128, false, true>(mq, mk, mv, a, n_seqs, max_len, stream);
 }

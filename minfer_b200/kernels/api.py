@@ -185,6 +185,10 @@ def _sig_attention_prefill_tc(lib: ctypes.CDLL) -> None:
                                                   [c_float, c_longlong, c_void_p, c_void_p])
 
 
+    lib.mf_sink_attention_tc.argtypes = ([c_void_p] * 6 + [c_int, c_int] + [c_void_p] * 3 + [c_int] * 9 +
+                                         [c_float, c_longlong, c_void_p, c_void_p])
+
+
 _SIGNATURES = {"attention_prefill_tc": _sig_attention_prefill_tc,
                "attention_sink": _sig_attention_sink,
                "attention_prefill": _sig_attention_prefill, "gemm_tc": _sig_gemm_tc, "ops": _sig_ops, "gemm_simt": _sig_gemm_simt, "attention": _sig_attention,
@@ -812,6 +816,33 @@ def sink_attention_mma(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seq
         _ptr(out, "out"), _f32(r1, "r1"), _f32(r2, "r2"), int(n_rows), int(max_row_tokens), n_heads,
         n_kv, head_dim, value_dim, int(window), int(chunk), 1 if sink else 0, float(scale),
         _stream()), "sink_attention_mma")
+
+
+def sink_attention_tc_supported(dtype: torch.dtype, head_dim: int, value_dim: int) -> bool:
+    """The tcgen05 kernel takes bfloat16 with keys and values of one size, 64 or 128."""
+    return dtype == torch.bfloat16 and head_dim == value_dim and head_dim in (64, 128)
+
+
+def sink_attention_tc(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: torch.Tensor,
+                      seq_end: Optional[torch.Tensor], page_table: Optional[torch.Tensor],
+                      table_stride: int, ring: int, out: torch.Tensor, r1: Optional[torch.Tensor],
+                      r2: Optional[torch.Tensor], n_rows: int, max_row_tokens: int, n_heads: int,
+                      n_kv: int, head_dim: int, window: int, chunk: int, sink: bool, scale: float,
+                      status: torch.Tensor) -> None:
+    """``sink_attention_mma``'s job on the 5th-generation tensor cores (tcgen05, tensor memory):
+    the step's packed queries over the step's own keys (``page_table`` None) or over the cache."""
+    n = q.shape[0]
+    if q.dtype != torch.bfloat16 or out.shape != (n, n_heads * head_dim):
+        raise KernelError("sink_attention_tc: bfloat16 only, out [tokens, heads * head size]")
+    if (r1 is None) != (r2 is None) or (page_table is None) != (seq_end is None):
+        raise KernelError("sink_attention_tc: inconsistent arguments")
+    pages = k.shape[0] if page_table is not None else 0
+    _check(_lib("attention_prefill_tc").mf_sink_attention_tc(
+        _ptr(q, "q"), _ptr(k, "k"), _ptr(v, "v"), _i32(cu_seqlens, "cu_seqlens"),
+        _i32(seq_end, "seq_end"), _i32(page_table, "page_table"), int(table_stride), int(ring),
+        _ptr(out, "out"), _f32(r1, "r1"), _f32(r2, "r2"), n, int(n_rows), int(max_row_tokens),
+        n_heads, n_kv, head_dim, int(window), int(chunk), 1 if sink else 0, float(scale), int(pages),
+        _i32(status, "status"), _stream()), "sink_attention_tc")
 
 
 _SINK_PLANS: dict = {}

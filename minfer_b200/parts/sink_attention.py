@@ -37,12 +37,23 @@ FORCE_GENERIC = os.environ.get("MINFER_B200_SINK_ATTENTION_GENERIC", "0") == "1"
 PAGED_PROMPT_MIN_TOKENS = int(os.environ.get("MINFER_B200_SINK_PAGED_PROMPT_MIN_TOKENS", "48"))
 
 
+# tiles of 128 queries pay from this many tokens on (as for the other attention mixer)
+PAGED_TCGEN05_MIN_TOKENS = int(os.environ.get("MINFER_B200_SINK_PAGED_TCGEN05_MIN_TOKENS", "160"))
+# "tcgen05" (tensor memory, where the sizes allow) or "mma" (the mma.sync kernel) for prompts
+PROMPT_KERNEL = os.environ.get("MINFER_B200_SINK_PROMPT_KERNEL", "tcgen05")
+
+
 class SinkAttention(Mixer):
     capturable = True      # launches kernels only; safe inside a CUDA graph capture
 
     def libraries(self, dtype: torch.dtype) -> List[str]:
         libs = ["ops", "attention_sink"]
-        libs.append("gemm_tc" if dtype == torch.bfloat16 else "gemm_simt")
+        if dtype == torch.bfloat16:
+            libs.append("gemm_tc")
+            if K.sink_attention_tc_supported(dtype, self.head_dim, self.value_dim):
+                libs.append("attention_prefill_tc")
+        else:
+            libs.append("gemm_simt")
         return libs
 
     def __init__(self, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int,
@@ -159,7 +170,14 @@ class SinkAttention(Mixer):
                             n_partials=n_partials)
         o = torch.empty((n, nh * vd), dtype=act, device=dev)
         tensor_cores = (K.sink_attention_mma_supported(act, hd, vd) and not FORCE_GENERIC)
-        if own_kv and tensor_cores:
+        # prompts: the tcgen05 kernel where keys and values have one size it takes, else mma.sync
+        tcgen05 = (tensor_cores and PROMPT_KERNEL != "mma"
+                   and K.sink_attention_tc_supported(act, hd, vd))
+        if own_kv and tcgen05:
+            K.sink_attention_tc(q, k_step, v_step, ctx.cu_seqlens, None, None, 0, 0, o, self.r1,
+                                self.r2, ctx.n_rows, ctx.max_row_tokens, nh, nk, hd, self.window,
+                                self.chunk, self.sink, self.scale, ctx.status)
+        elif own_kv and tensor_cores:
             K.sink_attention_mma(q, k_step, v_step, ctx.cu_seqlens, None, None, 0, 0, o, self.r1,
                                  self.r2, ctx.n_rows, ctx.max_row_tokens, nh, nk, hd, vd,
                                  self.window, self.chunk, self.sink, self.scale)
@@ -174,6 +192,13 @@ class SinkAttention(Mixer):
                     f"a sequence brings {ctx.max_row_tokens} tokens, but a ring of {cache.ring} "
                     f"positions with a reach of {reach} takes {cache.ring - reach + 1} a step "
                     f"(the engine runs longer rows in portions)")
+            if tcgen05 and not ctx.single_token and ctx.n_tokens >= PAGED_TCGEN05_MIN_TOKENS:
+                K.sink_attention_tc(q, cache.k, cache.v, ctx.cu_seqlens, ctx.seq_end,
+                                    cache.page_table, cache.table_stride, cache.ring, o, self.r1,
+                                    self.r2, ctx.n_rows, ctx.max_row_tokens, nh, nk, hd,
+                                    self.window, self.chunk, self.sink, self.scale, ctx.status)
+                self._project_out(o, ctx, residual)
+                return
             if tensor_cores and not ctx.single_token and ctx.n_tokens >= PAGED_PROMPT_MIN_TOKENS:
                 # rows of several tokens: query tiles of the step's rows over the cache's pages
                 K.sink_attention_mma(q, cache.k, cache.v, ctx.cu_seqlens, ctx.seq_end,

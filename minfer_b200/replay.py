@@ -64,12 +64,13 @@ def main(argv=None) -> int:
                 slots.append(slot_of[rid])
                 tokens.append([int(t) for t in e["tokens"]])
                 held[rid] = held.get(rid, 0) + len(tokens[-1])
-            if sum(held.values()) > args.max_tokens:
+                want.append([int(x) for x in e.get("want", [])])
+            # (a caller that counts in pages may already have rounded each request up)
+            if sum(held.values()) > args.max_tokens + 64 * len(held):
                 from .cache.paged import OutOfPages
                 raise OutOfPages(
                     f"the cache has no free page left: live requests would hold "
                     f"{sum(held.values())} tokens, --max-tokens is {args.max_tokens}")
-                want.append([int(x) for x in e.get("want", [])])
             logits = engine.step(slots, tokens, want)
             if logits.shape[0] > 0:
                 data = logits.to(torch.float32).cpu().contiguous().numpy().astype("<f4")

@@ -409,3 +409,70 @@ def test_single_query_kernel_on_tensor_cores(case, ringed, sink):
                               stride, ring, out1, r1.float().to(DEV), r2.float().to(DEV), heads, kv, hd,
                               vd, 0, chunk, sink, 0.3, reach)
     assert _err(out1, want_all[[rows[-1]]]) < 2e-2
+
+
+TC_CASES = [  # heads, kv, hd, chunk, lengths   (keys and values of one size, 64 or 128)
+    (8, 2, 64, 200, [401, 200, 201, 1]),
+    (4, 4, 128, 128, [129, 257, 600]),
+    (4, 2, 64, 5000, [300]),
+    (2, 1, 128, 0, [700, 17]),
+    (2, 2, 64, 1, [70]),
+    (6, 3, 128, 96, [333, 95, 97]),
+]
+
+
+@pytest.mark.parametrize("case", TC_CASES)
+@pytest.mark.parametrize("bias, sink", [(True, True), (False, True), (True, False)])
+def test_prompt_kernel_tcgen05_packed(case, bias, sink):
+    heads, kv, hd, chunk, lengths = case
+    q, k, v, r1, r2 = _qkv_case(11 * hd, heads, kv, hd, hd, lengths)
+    _spike(q, k, v, lengths, chunk, heads // kv)
+    if not bias:
+        r1 = r2 = torch.zeros(heads, dtype=torch.float64)
+    t = torch.bfloat16
+    qd, kd, vd_ = q.to(t).to(DEV), k.to(t).to(DEV), v.to(t).to(DEV)
+    want = _plain_rows(qd.double().cpu(), kd.double().cpu(), vd_.double().cpu(), r1, r2, 0.3, chunk, lengths)
+    if not sink:
+        ones = _plain_rows(qd.double().cpu(), kd.double().cpu(), torch.ones_like(vd_).double().cpu(), r1,
+                           r2, 0.3, chunk, lengths)
+        want = (want.view(-1, heads, hd) / ones.view(-1, heads, hd)[..., :1]).reshape(want.shape)
+    cu = [0]
+    for n in lengths:
+        cu.append(cu[-1] + n)
+    out = torch.empty(sum(lengths), heads * hd, dtype=t, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    f = lambda x: x.float().to(DEV) if bias else None
+    K().sink_attention_tc(qd, kd, vd_, _i32(cu), None, None, 0, 0, out, f(r1), f(r2), len(lengths),
+                          max(lengths), heads, kv, hd, 0, chunk, sink, 0.3, status)
+    assert int(status.item()) == 0
+    assert _err(out, want) < 2e-2
+
+
+@pytest.mark.parametrize("case", TC_CASES)
+@pytest.mark.parametrize("ringed", [False, True])
+def test_prompt_kernel_tcgen05_over_pages(case, ringed):
+    heads, kv, hd, chunk, lengths = case
+    if ringed and (chunk == 0 or chunk > 1000):
+        pytest.skip("a ring needs a bound on how far a query looks back")
+    q, k, v, r1, r2 = _qkv_case(13 * hd, heads, kv, hd, hd, lengths)
+    _spike(q, k, v, lengths, chunk, heads // kv)
+    t = torch.bfloat16
+    qd, kd, vd_ = q.to(t), k.to(t), v.to(t)
+    want_all = _plain_rows(qd.double(), kd.double(), vd_.double(), r1, r2, 0.3, chunk, lengths)
+    tail_max = 170
+    ring = -(-(chunk + tail_max - 1) // 64) * 64 if ringed else 0
+    kc, vc, table, stride = _paged(kd, vd_, lengths, ring, seed=hd + 3)
+    rows, cu, at = [], [0], 0
+    for n in lengths:
+        tail = min(n, tail_max)
+        rows += list(range(at + n - tail, at + n))
+        cu.append(cu[-1] + tail)
+        at += n
+    out = torch.empty(len(rows), heads * hd, dtype=t, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    K().sink_attention_tc(qd[rows].contiguous().to(DEV), kc.to(DEV), vc.to(DEV), _i32(cu), _i32(lengths),
+                          table.reshape(-1).to(DEV), stride, ring, out, r1.float().to(DEV),
+                          r2.float().to(DEV), len(lengths), tail_max, heads, kv, hd, 0, chunk, True, 0.3,
+                          status)
+    assert int(status.item()) == 0
+    assert _err(out, want_all[rows]) < 2e-2

@@ -404,6 +404,10 @@ def furitar_attention_kernels(torch, K, pk, heads, kv, dim, chunk, tokens=2048, 
     ms_f = _median_ms(torch, lambda: K.sink_attention_mma(q, k, v, cu, None, None, 0, 0, o, r1, r2, 1,
                                                           tokens, heads, kv, dim, dim, 0, chunk, True,
                                                           scale), flush=flush)
+    ms_f_mma = ms_f
+    ms_f = _median_ms(torch, lambda: K.sink_attention_tc(q, k, v, cu, None, None, 0, 0, o, r1, r2, 1,
+                                                         tokens, heads, kv, dim, 0, chunk, True, scale,
+                                                         status), flush=flush)
     ms_q = _median_ms(torch, lambda: K.attention_prefill_tc(q, k, v, cu, o, 1, tokens, heads, kv, dim, 0,
                                                             scale, status), flush=flush)
     full, rest = divmod(tokens, chunk)
@@ -412,6 +416,7 @@ def furitar_attention_kernels(torch, K, pk, heads, kv, dim, chunk, tokens=2048, 
     peak = pk["bf16_tflops"] * 1e12
     out["prompt"] = {
         "furitar_us": round(ms_f * 1e3, 1), "qwen2_us": round(ms_q * 1e3, 1),
+        "furitar_mma_sync_us": round(ms_f_mma * 1e3, 1),
         "furitar_frac": round(heads * 4 * dim * pairs_f / (ms_f * 1e-3) / peak, 4),
         "qwen2_frac": round(heads * 4 * dim * pairs_q / (ms_q * 1e-3) / peak, 4)}
     # single queries over pages

@@ -74,17 +74,36 @@ unit_norm_kvstore_kernel(const float* __restrict__ qkv, int n_partials, int n_to
                                          : (size_t)(n_heads + hk) * hd);
         float val[SA_MAX_D / 32];
         float ss = 0.0f;
+        if (n_partials <= 16) {
+            // all splits' loads of a head in flight at once (a split beyond n_partials reads the
+            // last one again and adds nothing); the sums keep the split order
+            const int last_split = max(n_partials, 1) - 1;
 #pragma unroll
-        for (int i = 0; i < SA_MAX_D / 32; ++i) {
-            const int d = lane + 32 * i;
-            float v = 0.0f;
-            if (d < width) {
-                v = in[col0 + d];
-                for (int sp = 1; sp < n_partials; ++sp) v += in[sp * plane + col0 + d];
+            for (int i = 0; i < SA_MAX_D / 32; ++i) val[i] = 0.0f;
+#pragma unroll
+            for (int sp = 0; sp < 16; ++sp) {
+                const float* src = in + (size_t)min(sp, last_split) * plane + col0;
+#pragma unroll
+                for (int i = 0; i < SA_MAX_D / 32; ++i) {
+                    const int d = lane + 32 * i;
+                    const float x = d < width ? src[d] : 0.0f;
+                    val[i] += sp <= last_split ? x : 0.0f;
+                }
             }
-            val[i] = v;
-            ss = fmaf(v, v, ss);
+        } else {
+#pragma unroll
+            for (int i = 0; i < SA_MAX_D / 32; ++i) {
+                const int d = lane + 32 * i;
+                float v = 0.0f;
+                if (d < width) {
+                    v = in[col0 + d];
+                    for (int sp = 1; sp < n_partials; ++sp) v += in[sp * plane + col0 + d];
+                }
+                val[i] = v;
+            }
         }
+#pragma unroll
+        for (int i = 0; i < SA_MAX_D / 32; ++i) ss = fmaf(val[i], val[i], ss);
         float f = 1.0f;
         if (!is_v && norm_qk) {
             ss = warp_sum(ss);

@@ -751,9 +751,14 @@ extern "C" int mf_add_rows(float* h, const void* table, int table_dtype, const i
 // written by norm_shift_save_kernel, launched behind this one (the block of a row's first
 // token reads the state while the block of its last would write it).
 // ------------------------------------------------------------------------------------
+// `partial` (may be null): the K splits [n_partials][tokens][width] of the projection before,
+// which this kernel adds into x first, with `bias`, in split order (x is then complete in
+// memory).  Only in steps in which every sequence brings one token: a row with a row above it
+// in the step would need that row complete too, which only its own block makes it.
 template <typename TO>
-__global__ void norm_shift_kernel(const float* __restrict__ x, const float* __restrict__ w,
-                                  const float* __restrict__ shift,
+__global__ void norm_shift_kernel(float* x, const float* __restrict__ partial, int n_partials,
+                                  const float* __restrict__ bias, int n_tokens,
+                                  const float* __restrict__ w, const float* __restrict__ shift,
                                   const int* __restrict__ positions,
                                   const int* __restrict__ token_row,
                                   const int* __restrict__ cu_seqlens,
@@ -768,15 +773,52 @@ __global__ void norm_shift_kernel(const float* __restrict__ x, const float* __re
     const bool last = t == cu_seqlens[b + 1] - 1;
     float* st = state + (size_t)slots[b] * width;
     pdl_wait();
-    const float* xr = x + (size_t)t * width;
+    float* xr = x + (size_t)t * width;
     const float* xp = xr - width;                       // the row above (used unless first)
     float ss = 0.0f, sp = 0.0f;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        const float v = xr[i];
-        ss = fmaf(v, v, ss);
-        if (!first) {
-            const float u = xp[i];
-            sp = fmaf(u, u, sp);
+    if (n_partials > 0) {
+        // every split's load of an element is in flight at once (a split beyond n_partials
+        // reads the last one again and adds nothing); the sums keep the split order
+        const size_t plane = (size_t)n_tokens * width;
+        const float* pr = partial + (size_t)t * width;
+        const int last_split = n_partials - 1;
+        if ((width & 3) == 0 && n_partials <= 16) {
+            for (int i = threadIdx.x; i < (width >> 2); i += blockDim.x) {
+                float4 v = reinterpret_cast<const float4*>(xr)[i];
+                float4 pv[16];
+#pragma unroll
+                for (int s = 0; s < 16; ++s)
+                    pv[s] = reinterpret_cast<const float4*>(pr + (size_t)min(s, last_split) * plane)[i];
+                if (bias != nullptr) {
+                    const float4 bv = reinterpret_cast<const float4*>(bias)[i];
+                    v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
+                }
+#pragma unroll
+                for (int s = 0; s < 16; ++s) {
+                    if (s < n_partials) { v.x += pv[s].x; v.y += pv[s].y; v.z += pv[s].z; v.w += pv[s].w; }
+                }
+                reinterpret_cast<float4*>(xr)[i] = v;       // read again below
+                ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss);
+                ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+            }
+            __syncthreads();                                // other threads read these elements below
+        } else {
+            for (int i = threadIdx.x; i < width; i += blockDim.x) {
+                float v = xr[i];
+                if (bias != nullptr) v += bias[i];
+                for (int s = 0; s < n_partials; ++s) v += pr[s * plane + i];
+                xr[i] = v;                                  // read again below by this same thread
+                ss = fmaf(v, v, ss);
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+            const float v = xr[i];
+            ss = fmaf(v, v, ss);
+            if (!first) {
+                const float u = xp[i];
+                sp = fmaf(u, u, sp);
+            }
         }
     }
     ss = block_sum(ss, scratch);
@@ -820,27 +862,31 @@ __global__ void norm_shift_save_kernel(const float* __restrict__ x, const float*
     for (int i = threadIdx.x; i < width; i += blockDim.x) st[i] = xr[i] * scale * w[i];
 }
 
-// `multi`: some row may bring more than one token (then the second kernel runs too)
-extern "C" int mf_norm_shift(const float* x, const float* w, const float* shift,
+// `multi`: some row may bring more than one token (then the second kernel runs too, and no
+// partial sums are taken)
+extern "C" int mf_norm_shift(float* x, const float* partial, int n_partials, const float* bias,
+                             const float* w, const float* shift,
                              const int* positions, const int* token_row, const int* cu_seqlens,
                              const int* slots, float* state, void* y, int out_dtype, int n_tokens,
                              int n_rows, int width, float eps, int multi, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
+    if (n_partials < 0 || (n_partials > 0 && (multi || partial == nullptr))) return MF_ERR_ARGUMENT;
     // the block size is a function of the width only, so a row's sum never depends on the batch
     int threads = 32;
     while (threads < 512 && threads * 4 < width) threads <<= 1;
     if (out_dtype == MF_DTYPE_F32)
-        mf_launch(norm_shift_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, x, w, shift,
-                  positions, token_row, cu_seqlens, slots, state, (float*)y, width, eps);
+        mf_launch(norm_shift_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, x, partial,
+                  n_partials, bias, n_tokens, w, shift, positions, token_row, cu_seqlens, slots, state,
+                  (float*)y, width, eps);
     else if (out_dtype == MF_DTYPE_BF16)
-        mf_launch(norm_shift_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, x, w,
-                  shift, positions, token_row, cu_seqlens, slots, state, (__nv_bfloat16*)y, width,
-                  eps);
+        mf_launch(norm_shift_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, x,
+                  partial, n_partials, bias, n_tokens, w, shift, positions, token_row, cu_seqlens, slots,
+                  state, (__nv_bfloat16*)y, width, eps);
     else
         return MF_ERR_UNSUPPORTED;
     if (multi)
-        mf_launch(norm_shift_save_kernel, dim3(n_rows), dim3(threads), 0, stream, x, w, cu_seqlens,
-                  slots, state, width, eps);
+        mf_launch(norm_shift_save_kernel, dim3(n_rows), dim3(threads), 0, stream, (const float*)x, w,
+                  cu_seqlens, slots, state, width, eps);
     return MF_LAUNCH_CHECK();
 }
 

@@ -107,8 +107,8 @@ def _sig_ops(lib: ctypes.CDLL) -> None:
     lib.mf_cast.argtypes = [c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p]
     lib.mf_add_rows.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p,
                                 c_void_p]
-    lib.mf_norm_shift.argtypes = [c_void_p] * 9 + [c_int, c_int, c_int, c_int, c_float, c_int,
-                                                   c_void_p]
+    lib.mf_norm_shift.argtypes = ([c_void_p, c_void_p, c_int] + [c_void_p] * 9 +
+                                  [c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
     lib.mf_xielu.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_longlong, c_void_p]
 
 
@@ -321,19 +321,27 @@ def add_rows(h: torch.Tensor, table: torch.Tensor, index: torch.Tensor, status: 
 
 def norm_shift(x: torch.Tensor, weight: torch.Tensor, shift: torch.Tensor, eps: float,
                positions: torch.Tensor, token_row: torch.Tensor, cu_seqlens: torch.Tensor,
-               slots: torch.Tensor, state: torch.Tensor, out: torch.Tensor, multi: bool) -> None:
+               slots: torch.Tensor, state: torch.Tensor, out: torch.Tensor, multi: bool,
+               partial: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None) -> None:
     """n = rmsnorm(x) * weight; out[t] = n[t] + (n[t-1] - n[t]) * shift, where n[t-1] of the
     first token a sequence brings is ``state[slot]`` (zeros at position 0); ``state[slot]``
     takes n of the last token a sequence brings.  ``multi``: some row may bring more than one
-    token."""
+    token.  ``partial`` [splits, tokens, width] (only without ``multi``): the K splits of the
+    projection before, added into ``x`` first, with ``bias``."""
     n, width = out.shape
     n_rows = slots.numel()
     if x.shape != (n, width) or weight.numel() != width or shift.numel() != width:
         raise KernelError("norm_shift: shapes do not fit")
     if state.dim() != 2 or state.shape[1] != width or cu_seqlens.numel() != n_rows + 1:
         raise KernelError("norm_shift: the state or the row bounds do not fit")
+    n_partials = 0
+    if partial is not None:
+        if multi or partial.dim() != 3 or partial.shape[1:] != (n, width):
+            raise KernelError("norm_shift: partial sums must be [splits, tokens, width], one token a row")
+        n_partials = partial.shape[0]
     _check(_lib("ops").mf_norm_shift(
-        _f32(x, "x"), _f32(weight, "weight"), _f32(shift, "shift"), _i32(positions, "positions"),
+        _f32(x, "x"), _f32(partial, "partial"), n_partials, _f32(bias, "bias"),
+        _f32(weight, "weight"), _f32(shift, "shift"), _i32(positions, "positions"),
         _i32(token_row, "token_row"), _i32(cu_seqlens, "cu_seqlens"), _i32(slots, "slots"),
         _f32(state, "state"), _ptr(out, "out"), dtype_code(out.dtype), n, n_rows, width, float(eps),
         1 if multi else 0, _stream()), "norm_shift", 2 if multi else 1)

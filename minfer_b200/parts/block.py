@@ -92,7 +92,6 @@ class PreNormBlock(Block):
     def mix(self, h: torch.Tensor, ctx: StepContext, binding: CallBinding) -> None:
         if self.shift is not None:
             ctx.extras.pop("prepared", None)
-            settle_pending(ctx, h)
             x, scale = self.shift.norm_and_shift(self.mixer_norm, h, ctx, binding.state), None
         else:
             x, scale = self._normed(self.mixer_norm, h, ctx, self.mixer)

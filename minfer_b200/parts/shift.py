@@ -44,12 +44,22 @@ class TokenShift(Part):
 
     def norm_and_shift(self, norm, h: torch.Tensor, ctx: StepContext,
                        state: Dict[str, torch.Tensor]) -> torch.Tensor:
-        """``norm`` must be y = x / rms * w (``Norm.foldable``)."""
+        """``norm`` must be y = x / rms * w (``Norm.foldable``).  A projection output that is
+        still pending (its K splits) is added into ``h`` here: by this kernel where every row
+        brings one token, else by the reduction kernel first."""
         fold = norm.foldable()
         if fold is None:
             raise K.KernelError("the token shift is fused with an RMS norm; this norm is another")
         weight, eps, size = fold
         out = torch.empty((h.shape[0], self.size), dtype=ctx.act_dtype, device=h.device)
+        pending = ctx.extras.pop("pending", None)
+        partial = bias = None
+        if pending is not None:
+            if ctx.single_token and pending.partial.dim() == 3:
+                partial, bias = pending.partial, pending.bias
+            else:
+                pending.settle(h)
         K.norm_shift(h, weight, self.weight, eps, ctx.positions, ctx.token_row, ctx.cu_seqlens,
-                     ctx.slots, state[STATE_NAME], out, multi=not ctx.single_token)
+                     ctx.slots, state[STATE_NAME], out, multi=not ctx.single_token,
+                     partial=partial, bias=bias)
         return out

@@ -72,6 +72,30 @@ def test_norm_and_shift_with_state(dtype, width):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_norm_and_shift_adds_pending_splits(dtype):
+    """One token a row: the K splits of the projection before are added into x by the kernel."""
+    g = torch.Generator().manual_seed(21)
+    width, rows = 136, 4
+    x = torch.randn(rows, width, generator=g).to(DEV)
+    parts = torch.randn(3, rows, width, generator=g).to(DEV)
+    bias = torch.randn(width, generator=g).to(DEV)
+    w = (1 + 0.1 * torch.randn(width, generator=g)).to(DEV)
+    s = (0.5 + 0.4 * torch.randn(width, generator=g)).to(DEV)
+    state = torch.randn(5, width, generator=g).to(DEV)
+    state0 = state.clone()
+    full = x.double().cpu() + parts.double().cpu().sum(0) + bias.double().cpu()
+    out = torch.empty(rows, width, dtype=DT[dtype], device=DEV)
+    K().norm_shift(x, w, s, 1e-5, _i32([3, 0, 9, 1]), _i32([0, 1, 2, 3]), _i32([0, 1, 2, 3, 4]),
+                   _i32([2, 0, 4, 1]), state, out, multi=False, partial=parts, bias=bias)
+    assert _err(x, full) < 3e-6                           # x is complete in memory afterwards
+    for b, (slot, pos) in enumerate(zip([2, 0, 4, 1], [3, 0, 9, 1])):
+        h = P.rms_norm(full[b:b + 1], w.double().cpu(), 1e-5)
+        before = state0[slot].double().cpu() if pos > 0 else torch.zeros(width, dtype=torch.float64)
+        assert _err(out[b:b + 1], P.token_shift(h, before, s.double().cpu())) < TOL[dtype]
+        assert _err(state[slot], h[-1]) < 3e-6
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_xielu(dtype):
     g = torch.Generator().manual_seed(1)
     z = (3 * torch.randn(37, 129, generator=g)).to(DEV)

@@ -74,7 +74,13 @@ unit_norm_kvstore_kernel(const float* __restrict__ qkv, int n_partials, int n_to
                                          : (size_t)(n_heads + hk) * hd);
         float val[SA_MAX_D / 32];
         float ss = 0.0f;
-        if (n_partials <= 16) {
+        if (n_partials <= 1) {                           // the projection's whole sums (prompts)
+#pragma unroll
+            for (int i = 0; i < SA_MAX_D / 32; ++i) {
+                const int d = lane + 32 * i;
+                val[i] = d < width ? in[col0 + d] : 0.0f;
+            }
+        } else if (n_partials <= 16) {
             // all splits' loads of a head in flight at once (a split beyond n_partials reads the
             // last one again and adds nothing); the sums keep the split order
             const int last_split = max(n_partials, 1) - 1;

@@ -755,7 +755,9 @@ extern "C" int mf_add_rows(float* h, const void* table, int table_dtype, const i
 // which this kernel adds into x first, with `bias`, in split order (x is then complete in
 // memory).  Only in steps in which every sequence brings one token: a row with a row above it
 // in the step would need that row complete too, which only its own block makes it.
-template <typename TO>
+// SPLITS: compiled with the addition of the K splits (kept out of the form for prompts, which
+// then needs few registers and shares an SM among several rows).
+template <typename TO, bool SPLITS>
 __global__ void norm_shift_kernel(float* x, const float* __restrict__ partial, int n_partials,
                                   const float* __restrict__ bias, int n_tokens,
                                   const float* __restrict__ w, const float* __restrict__ shift,
@@ -776,7 +778,7 @@ __global__ void norm_shift_kernel(float* x, const float* __restrict__ partial, i
     float* xr = x + (size_t)t * width;
     const float* xp = xr - width;                       // the row above (used unless first)
     float ss = 0.0f, sp = 0.0f;
-    if (n_partials > 0) {
+    if (SPLITS && n_partials > 0) {
         // every split's load of an element is in flight at once (a split beyond n_partials
         // reads the last one again and adds nothing); the sums keep the split order
         const size_t plane = (size_t)n_tokens * width;
@@ -874,16 +876,18 @@ extern "C" int mf_norm_shift(float* x, const float* partial, int n_partials, con
     // the block size is a function of the width only, so a row's sum never depends on the batch
     int threads = 32;
     while (threads < 512 && threads * 4 < width) threads <<= 1;
-    if (out_dtype == MF_DTYPE_F32)
-        mf_launch(norm_shift_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, x, partial,
-                  n_partials, bias, n_tokens, w, shift, positions, token_row, cu_seqlens, slots, state,
-                  (float*)y, width, eps);
-    else if (out_dtype == MF_DTYPE_BF16)
-        mf_launch(norm_shift_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, x,
-                  partial, n_partials, bias, n_tokens, w, shift, positions, token_row, cu_seqlens, slots,
-                  state, (__nv_bfloat16*)y, width, eps);
-    else
+#define MF_NORM_SHIFT(TO, SPLITS) \
+    mf_launch(norm_shift_kernel<TO, SPLITS>, dim3(n_tokens), dim3(threads), 0, stream, x, partial, \
+              n_partials, bias, n_tokens, w, shift, positions, token_row, cu_seqlens, slots, state, \
+              (TO*)y, width, eps)
+    if (out_dtype == MF_DTYPE_F32) {
+        if (n_partials > 0) MF_NORM_SHIFT(float, true); else MF_NORM_SHIFT(float, false);
+    } else if (out_dtype == MF_DTYPE_BF16) {
+        if (n_partials > 0) MF_NORM_SHIFT(__nv_bfloat16, true); else MF_NORM_SHIFT(__nv_bfloat16, false);
+    } else {
         return MF_ERR_UNSUPPORTED;
+    }
+#undef MF_NORM_SHIFT
     if (multi)
         mf_launch(norm_shift_save_kernel, dim3(n_rows), dim3(threads), 0, stream, (const float*)x, w,
                   cu_seqlens, slots, state, width, eps);

@@ -310,7 +310,7 @@ MMA_CASES = [  # heads, kv, hd, vd, chunk, lengths
     (8, 2, 64, 64, 200, [401, 200, 201, 1]),
     (16, 1, 64, 128, 150, [310, 64]),
     (4, 4, 128, 128, 128, [129, 257]),
-    (6, 2, 48, 80, 96, [333, 95, 97]),
+    (6, 2, 48, 72, 88, [333, 87, 89]),
     (2, 1, 128, 40, 64, [191]),
     (4, 2, 8, 8, 1, [70]),
     (3, 1, 104, 56, 0, [500, 17]),
@@ -441,7 +441,7 @@ TC_CASES = [  # heads, kv, hd, chunk, lengths   (keys and values of one size, 64
     (4, 2, 64, 5000, [300]),
     (2, 1, 128, 0, [700, 17]),
     (2, 2, 64, 1, [70]),
-    (6, 3, 128, 96, [333, 95, 97]),
+    (6, 3, 128, 88, [333, 87, 89]),
 ]
 
 

@@ -43,7 +43,16 @@ FUR_C = {
                _layer(_att(4, 4, 128, 128, 0.15, 128), 384),
                _layer(_att(16, 1, 64, 128, 0.2, 150), 128)],
 }
-CASES = {"A": (FUR_A, 11), "B": (FUR_B, 12), "C": (FUR_C, 13)}
+# sizes that are multiples of nothing: a width the vector kernels do not take, five heads of ten,
+# more than 16 query heads on one key/value head, and a last layer without a feed-forward
+FUR_D = {
+    "architecture": "Furitar", "vocab": 77, "width": 90, "max_positions": 300,
+    "embedding": {"scale": 0.5}, "norm": {"eps": 1e-4}, "logit_scale": 2.0,
+    "layers": [_layer(_att(5, 5, 10, 6, 0.6, 7), 33),
+               _layer(_att(20, 1, 16, 8, 0.3, 50), 18),
+               _layer(_att(3, 1, 30, 14, 0.35, 129))],
+}
+CASES = {"A": (FUR_A, 11), "B": (FUR_B, 12), "C": (FUR_C, 13), "D": (FUR_D, 14)}
 
 
 def make_folder(name: str) -> str:

@@ -15,7 +15,7 @@ pytestmark = pytest.mark.gpu
 LENGTHS = [37, 5, 131, 64, 1, 65, 11]
 
 
-@pytest.fixture(scope="module", params=["A", "B", "C"])
+@pytest.fixture(scope="module", params=["A", "B", "C", "D"])
 def case(request):
     folder = make_folder(request.param)
     cfg, w = P.load_folder(folder)

@@ -30,7 +30,8 @@
 // ------------------------------------------------------------------------------------------
 // q and k to unit root mean square per head, cache write
 // ------------------------------------------------------------------------------------------
-template <typename T>
+// NI: 32-element groups of a head a lane may hold (sizes up to 32 * NI)
+template <typename T, int NI>
 __global__ void __launch_bounds__(SA_WARPS * 32)
 unit_norm_kvstore_kernel(const float* __restrict__ qkv, int n_partials, int n_tokens,
                          const int* __restrict__ positions, const int* __restrict__ token_row,
@@ -72,11 +73,11 @@ unit_norm_kvstore_kernel(const float* __restrict__ qkv, int n_partials, int n_to
         const size_t col0 = is_q ? (size_t)item * hd
                                  : (is_v ? (size_t)(n_heads + n_kv) * hd + (size_t)hk * vd
                                          : (size_t)(n_heads + hk) * hd);
-        float val[SA_MAX_D / 32];
+        float val[NI];
         float ss = 0.0f;
         if (n_partials <= 1) {                           // the projection's whole sums (prompts)
 #pragma unroll
-            for (int i = 0; i < SA_MAX_D / 32; ++i) {
+            for (int i = 0; i < NI; ++i) {
                 const int d = lane + 32 * i;
                 val[i] = d < width ? in[col0 + d] : 0.0f;
             }
@@ -84,21 +85,26 @@ unit_norm_kvstore_kernel(const float* __restrict__ qkv, int n_partials, int n_to
             // all splits' loads of a head in flight at once (a split beyond n_partials reads the
             // last one again and adds nothing); the sums keep the split order
             const int last_split = max(n_partials, 1) - 1;
-#pragma unroll
-            for (int i = 0; i < SA_MAX_D / 32; ++i) val[i] = 0.0f;
+            float part[16][NI];
 #pragma unroll
             for (int sp = 0; sp < 16; ++sp) {
                 const float* src = in + (size_t)min(sp, last_split) * plane + col0;
 #pragma unroll
-                for (int i = 0; i < SA_MAX_D / 32; ++i) {
+                for (int i = 0; i < NI; ++i) {
                     const int d = lane + 32 * i;
-                    const float x = d < width ? src[d] : 0.0f;
-                    val[i] += sp <= last_split ? x : 0.0f;
+                    part[sp][i] = d < width ? src[d] : 0.0f;
                 }
+            }
+#pragma unroll
+            for (int i = 0; i < NI; ++i) val[i] = 0.0f;
+#pragma unroll
+            for (int sp = 0; sp < 16; ++sp) {
+#pragma unroll
+                for (int i = 0; i < NI; ++i) val[i] += sp <= last_split ? part[sp][i] : 0.0f;
             }
         } else {
 #pragma unroll
-            for (int i = 0; i < SA_MAX_D / 32; ++i) {
+            for (int i = 0; i < NI; ++i) {
                 const int d = lane + 32 * i;
                 float v = 0.0f;
                 if (d < width) {
@@ -109,7 +115,7 @@ unit_norm_kvstore_kernel(const float* __restrict__ qkv, int n_partials, int n_to
             }
         }
 #pragma unroll
-        for (int i = 0; i < SA_MAX_D / 32; ++i) ss = fmaf(val[i], val[i], ss);
+        for (int i = 0; i < NI; ++i) ss = fmaf(val[i], val[i], ss);
         float f = 1.0f;
         if (!is_v && norm_qk) {
             ss = warp_sum(ss);
@@ -127,7 +133,7 @@ unit_norm_kvstore_kernel(const float* __restrict__ qkv, int n_partials, int n_to
                        (((size_t)page * n_kv + hk) * MF_PAGE + (pos & (MF_PAGE - 1))) * width;
         }
 #pragma unroll
-        for (int i = 0; i < SA_MAX_D / 32; ++i) {
+        for (int i = 0; i < NI; ++i) {
             const int d = lane + 32 * i;
             if (d < width) {
                 const T y = from_f32<T>(val[i] * f);
@@ -156,14 +162,21 @@ extern "C" int mf_unit_norm_kvstore(const float* qkv, int n_partials, const int*
         if (by > 16) by = 16;
     }
     dim3 grid(n_tokens, by);
-#define MF_UNK(T) \
-    mf_launch(unit_norm_kvstore_kernel<T>, grid, dim3(SA_WARPS * 32), 0, stream, qkv, n_partials, \
+#define MF_UNK(T, NI) \
+    mf_launch(unit_norm_kvstore_kernel<T, NI>, grid, dim3(SA_WARPS * 32), 0, stream, qkv, n_partials, \
               n_tokens, positions, token_row, seq_end, (T*)q_out, (T*)k_out, (T*)v_out, \
               (T*)k_cache, (T*)v_cache, page_table, table_stride, ring, n_heads, n_kv, hd, vd, eps, \
               norm_qk, status)
-    if (dtype == MF_DTYPE_F32) MF_UNK(float);
-    else if (dtype == MF_DTYPE_BF16) MF_UNK(__nv_bfloat16);
+#define MF_UNK_SIZES(T) \
+    do { \
+        if (widest <= 32) MF_UNK(T, 1); else if (widest <= 64) MF_UNK(T, 2); \
+        else if (widest <= 128) MF_UNK(T, 4); else MF_UNK(T, 8); \
+    } while (0)
+    const int widest = hd > vd ? hd : vd;
+    if (dtype == MF_DTYPE_F32) MF_UNK_SIZES(float);
+    else if (dtype == MF_DTYPE_BF16) MF_UNK_SIZES(__nv_bfloat16);
     else return MF_ERR_UNSUPPORTED;
+#undef MF_UNK_SIZES
 #undef MF_UNK
     return MF_LAUNCH_CHECK();
 }

@@ -13,37 +13,69 @@
 // embedding: out[t][:] = table[ids[t]][:] * scale  (float32 out: the residual stream is
 // float32; scale is 1 for architectures that do not multiply their embeddings)
 // ------------------------------------------------------------------------------------
-template <typename T>
+// `rows` (may be null): a second table [n_rows_table][width] of which row row_idx[t] is added,
+// unscaled (learned position vectors: row_idx = the tokens' positions); an index outside it sets
+// MF_STATUS_BAD_POSITION and adds nothing.
+template <typename T, typename TR>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                              float* __restrict__ out, int width, int vocab, float scale,
-                             unsigned* __restrict__ status) {
+                             const TR* __restrict__ rows, const int* __restrict__ row_idx,
+                             int n_rows_table, unsigned* __restrict__ status) {
     pdl_prologue();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (size_t)t * width;
+    const TR* extra = nullptr;
+    if (rows != nullptr) {
+        const int r = row_idx[t];
+        if (r < 0 || r >= n_rows_table) {
+            if (threadIdx.x == 0) atomicOr(status, MF_STATUS_BAD_POSITION);
+        } else {
+            extra = rows + (size_t)r * width;
+        }
+    }
     if (id < 0 || id >= vocab) {
         if (threadIdx.x == 0) atomicOr(status, MF_STATUS_BAD_TOKEN);
         for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = 0.0f;
         return;
     }
     const T* row = table + (size_t)id * width;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = to_f32(row[i]) * scale;
+    if (extra != nullptr) {
+        for (int i = threadIdx.x; i < width; i += blockDim.x)
+            o[i] = fmaf(to_f32(row[i]), scale, 0.0f) + to_f32(extra[i]);
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = to_f32(row[i]) * scale;
+    }
+}
+
+extern "C" int mf_embed_rows(const void* table, int table_dtype, const int* ids, float* out,
+                             int n_tokens, int width, int vocab, float scale, const void* rows,
+                             int rows_dtype, const int* row_idx, int n_rows_table,
+                             unsigned* status, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (rows != nullptr && row_idx == nullptr) return MF_ERR_ARGUMENT;
+    const int threads = width >= 1024 ? 256 : 128;
+#define MF_EMBED(T, TR) \
+    mf_launch(embed_kernel<T, TR>, dim3(n_tokens), dim3(threads), 0, stream, (const T*)table, ids, out, \
+              width, vocab, scale, (const TR*)rows, row_idx, n_rows_table, status)
+    const bool rows_f32 = rows == nullptr || rows_dtype == MF_DTYPE_F32;
+    if (rows != nullptr && rows_dtype != MF_DTYPE_F32 && rows_dtype != MF_DTYPE_BF16) return MF_ERR_UNSUPPORTED;
+    if (table_dtype == MF_DTYPE_F32) {
+        if (rows_f32) MF_EMBED(float, float); else MF_EMBED(float, __nv_bfloat16);
+    } else if (table_dtype == MF_DTYPE_BF16) {
+        if (rows_f32) MF_EMBED(__nv_bfloat16, float); else MF_EMBED(__nv_bfloat16, __nv_bfloat16);
+    } else {
+        return MF_ERR_UNSUPPORTED;
+    }
+#undef MF_EMBED
+    return MF_LAUNCH_CHECK();
 }
 
 extern "C" int mf_embed(const void* table, int table_dtype, const int* ids, float* out,
                         int n_tokens, int width, int vocab, float scale, unsigned* status,
                         cudaStream_t stream) {
-    if (n_tokens <= 0) return 0;
-    const int threads = width >= 1024 ? 256 : 128;
-    if (table_dtype == MF_DTYPE_F32)
-        mf_launch(embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, (const float*)table, ids, out, width,
-                                                             vocab, scale, status);
-    else if (table_dtype == MF_DTYPE_BF16)
-        mf_launch(embed_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, 
-            (const __nv_bfloat16*)table, ids, out, width, vocab, scale, status);
-    else
-        return MF_ERR_UNSUPPORTED;
-    return MF_LAUNCH_CHECK();
+    return mf_embed_rows(table, table_dtype, ids, out, n_tokens, width, vocab, scale, nullptr, 0,
+                         nullptr, 0, status, stream);
 }
 
 // ------------------------------------------------------------------------------------

@@ -487,9 +487,14 @@ class Engine:
         model, plan = self.model, self.model.plan
         gemm.use_status_word(self.status)           # this engine's products report into its word
         h = torch.empty((ctx.n_tokens, plan.hidden_size), dtype=torch.float32, device=self.device)
-        K.embed(model.embedding, ctx.token_ids, h, self.status, plan.embedding_scale)
-        if model.after_embedding is not None:
-            model.after_embedding.forward_inplace(h, ctx)
+        added = model.after_embedding.embedding_rows(ctx) if model.after_embedding is not None else None
+        if added is not None:           # a table's rows by index (positions): the same kernel adds them
+            K.embed(model.embedding, ctx.token_ids, h, self.status, plan.embedding_scale,
+                    rows=added[0], row_index=added[1])
+        else:
+            K.embed(model.embedding, ctx.token_ids, h, self.status, plan.embedding_scale)
+            if model.after_embedding is not None:
+                model.after_embedding.forward_inplace(h, ctx)
         bindings = self._bindings(ctx)
         last = len(plan.schedule) - 1
         n_want = 0 if want_rows is None else want_rows.numel()

@@ -96,6 +96,8 @@ def _lib(name: str) -> ctypes.CDLL:
 def _sig_ops(lib: ctypes.CDLL) -> None:
     lib.mf_embed.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
                              c_void_p, c_void_p]
+    lib.mf_embed_rows.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
+                                  c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p]
     lib.mf_rmsnorm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
                                c_void_p]
     lib.mf_rope_kvstore.argtypes = ([c_void_p, c_int, c_void_p] + [c_void_p] * 10 + [c_int] * 9 +
@@ -199,12 +201,23 @@ _SIGNATURES = {"attention_prefill_tc": _sig_attention_prefill_tc,
 # row-wise ops
 # ---------------------------------------------------------------------------------------
 def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
-          scale: float = 1.0) -> None:
-    """out[t] = table[ids[t]] * scale in float32; an id outside the table sets status bit 1."""
+          scale: float = 1.0, rows: Optional[torch.Tensor] = None,
+          row_index: Optional[torch.Tensor] = None) -> None:
+    """out[t] = table[ids[t]] * scale in float32; an id outside the table sets status bit 1.
+    ``rows`` [m, width] with ``row_index`` [tokens]: out[t] += rows[row_index[t]] (unscaled; an
+    index outside sets status bit 2 and adds nothing)."""
     n, width = out.shape
     vocab = table.shape[0]
     if table.shape[1] != width or ids.numel() != n:
         raise KernelError("embed: shapes do not fit")
+    if rows is not None:
+        if row_index is None or row_index.numel() != n or rows.dim() != 2 or rows.shape[1] != width:
+            raise KernelError("embed: the added rows do not fit")
+        _check(_lib("ops").mf_embed_rows(
+            _ptr(table, "table"), dtype_code(table.dtype), _i32(ids, "ids"), _f32(out, "out"), n,
+            width, vocab, float(scale), _ptr(rows, "rows"), dtype_code(rows.dtype),
+            _i32(row_index, "row_index"), rows.shape[0], _i32(status, "status"), _stream()), "embed")
+        return
     _check(_lib("ops").mf_embed(_ptr(table, "table"), dtype_code(table.dtype), _i32(ids, "ids"),
                                 _f32(out, "out"), n, width, vocab, float(scale),
                                 _i32(status, "status"), _stream()), "embed")

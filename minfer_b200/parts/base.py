@@ -173,6 +173,12 @@ class ModelPart(Part):
     def forward_inplace(self, x: torch.Tensor, ctx: "StepContext") -> None:
         raise NotImplementedError
 
+    def embedding_rows(self, ctx: "StepContext"):
+        """For a part that runs after the embedding and only adds a table's rows to the residual
+        stream: (table [m, width], index int32 [tokens]), which the embedding kernel then adds
+        itself (``forward_inplace`` is not called); None for any other part."""
+        return None
+
 
 class Norm(Part):
     def forward(self, x32: torch.Tensor, out_dtype: torch.dtype,

@@ -37,3 +37,6 @@ class LearnedPositions(ModelPart):
 
     def forward_inplace(self, h: torch.Tensor, ctx: StepContext) -> None:
         K.add_rows(h, self.table, ctx.positions, ctx.status)
+
+    def embedding_rows(self, ctx: StepContext):
+        return self.table, ctx.positions

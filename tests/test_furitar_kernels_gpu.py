@@ -500,3 +500,19 @@ def test_prompt_kernel_tcgen05_over_pages(case, ringed):
                           status)
     assert int(status.item()) == 0
     assert _err(out, want_all[rows]) < 2e-2
+
+
+@pytest.mark.parametrize("table_dtype", ["float32", "bfloat16"])
+def test_embedding_adds_position_rows_itself(table_dtype):
+    g = torch.Generator().manual_seed(8)
+    t = DT[table_dtype]
+    table = torch.randn(40, 72, generator=g).to(t).to(DEV)
+    rows = torch.randn(50, 72, generator=g).to(t).to(DEV)
+    ids, pos = [3, 39, 0, 7], [0, 49, 12, 12]
+    out = torch.empty(4, 72, dtype=torch.float32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    K().embed(table, _i32(ids), out, status, 1.7, rows=rows, row_index=_i32(pos))
+    want = table[ids].float() * 1.7 + rows[pos].float()
+    assert torch.equal(out, want) and int(status.item()) == 0
+    K().embed(table, _i32(ids), out, status, 1.7, rows=rows, row_index=_i32([0, 50, 12, 12]))
+    assert int(status.item()) & 2 and torch.equal(out[1], table[39].float() * 1.7)

@@ -773,6 +773,7 @@ struct SinkDecodeArgs {
     const float* r2;
     int n_heads, n_kv, hd, vd, window, chunk, sink;
     int tiles_per_cta, n_splits;
+    int n_bufs;               // buffers a warp has: 2, or 1 when it takes one tile only
     float scale_log2;
 };
 
@@ -818,7 +819,7 @@ __global__ void __launch_bounds__(SD_WARPS * 32) sink_attention_decode_kernel(Si
     }
     pdl_wait();
 
-    const uint32_t my_s = (uint32_t)__cvta_generic_to_shared(sd_smem) + (uint32_t)(warp * 2 * TILE_BYTES);
+    const uint32_t my_s = (uint32_t)__cvta_generic_to_shared(sd_smem) + (uint32_t)(warp * a.n_bufs * TILE_BYTES);
     auto load_tile = [&](int tile, int buf) {
         const int key0 = tile * SD_KEYS;
         const int p_eff = a.ring > 0 ? key0 % a.ring : key0;
@@ -1039,13 +1040,16 @@ extern "C" int mf_sink_decode_plan(int rows, int n_kv, int reach_keys, int* tile
 
 template <int HDP, int VDP>
 static int launch_sink_decode(const SinkDecodeArgs& a, int rows, cudaStream_t stream) {
-    constexpr int tiles = SD_WARPS * 2 * SD_KEYS * (HDP + VDP) * 2;
+    constexpr int most = SD_WARPS * 2 * SD_KEYS * (HDP + VDP) * 2;
     constexpr int merge = SD_WARPS * 16 * (VDP + 4) * 4 + SD_WARPS * 16 * 2 * 4;
-    constexpr int smem = tiles > merge ? tiles : merge;
+    // a warp with one tile needs one buffer: half the shared memory, twice the CTAs on an SM
+    const int tiles = SD_WARPS * a.n_bufs * SD_KEYS * (HDP + VDP) * 2;
+    const int smem = tiles > merge ? tiles : merge;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(sink_attention_decode_kernel<HDP, VDP>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             most > merge ? most : merge);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
@@ -1078,6 +1082,7 @@ extern "C" int mf_sink_attention_decode(const void* q, const void* k_cache, cons
     a.sink = sink ? 1 : 0;
     a.scale_log2 = scale * 1.4426950408889634f;
     mf_sink_decode_plan(rows, n_kv, reach_keys, &a.tiles_per_cta, &a.n_splits);
+    a.n_bufs = a.tiles_per_cta > SD_WARPS ? 2 : 1;
     if (a.n_splits > 1 && partial == nullptr) return MF_ERR_ARGUMENT;
     int e;
     if (hd <= 64) e = vd <= 64 ? launch_sink_decode<64, 64>(a, rows, stream)

@@ -200,3 +200,77 @@ def test_greedy_generation_through_the_generator(case, dtype):
             slack = 0.05 * float(logits.abs().max())
             assert float(logits[tok]) >= float(logits.max()) - slack
             ids.append(tok)
+
+
+def test_command_line_generates(capsys):
+    from minfer_b200 import cli
+    folder = make_folder("B")
+    cfg, w = P.load_folder(folder)
+    rc = cli.main([folder, "5,17,3", "--greedy", "--repeat-penalty", "1.0", "-n", "6",
+                   "--dtype", "float32", "--stop", "100000"])
+    out = capsys.readouterr().out
+    assert rc == 0
+    want = P.generate_greedy(cfg, w, [5, 17, 3], 6)
+    assert " ".join(str(t) for t in want) in out
+    assert "Prefill: 3 tokens" in out and "Generated: 6 tokens" in out
+
+
+def test_sampled_generation_is_reproducible_and_independent_of_the_batch():
+    """Temperature sampling through the generator: the same seed gives the same tokens, alone or
+    beside other requests (float32: the logits are the same bits in both)."""
+    from minfer_b200.engine.generate import Generator
+    from minfer_b200.model import Model
+    from minfer_b200.sampling.params import SamplingParams
+    folder = make_folder("A")
+    cfg, _ = P.load_folder(folder)
+    prompts = [random_ids(n, cfg["vocab"], 900 + n) for n in (12, 30, 5)]
+    model = Model.from_folder(folder, "float32", "cuda:0")
+    sp = SamplingParams(0.8, 20, 0.95, 1.1, 0.0, 0.0, 1234)
+    together = Generator(model, max_tokens=2048, max_batch=3).generate(prompts, 10, sp, stop_token_ids=[])
+    again = Generator(model, max_tokens=2048, max_batch=3).generate(prompts, 10, sp, stop_token_ids=[])
+    assert [r.tokens for r in together] == [r.tokens for r in again]
+    assert all(len(r.tokens) == 10 and all(0 <= t < cfg["vocab"] for t in r.tokens) for r in together)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_replay_as_a_process(dtype):
+    """``bin/trace_run`` on a Furitar folder: whole prompts, then one request's last tokens one by
+    one beside another that ends earlier; logits files against the plain implementation."""
+    import json
+    import os
+    import subprocess
+    import sys
+    import tempfile
+    import numpy as np
+    folder = make_folder("D")
+    cfg, w = P.load_folder(folder)
+    a, b = random_ids(70, cfg["vocab"], 1), random_ids(9, cfg["vocab"], 2)
+    plain = {"a": P.forward(cfg, w, a)[0], "b": P.forward(cfg, w, b)[0]}
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:60], "want": [0, 59]},
+                                     {"id": "b", "tokens": b[:7], "want": [6]}], "end": []}]
+    expect = {0: [("a", [0, 59]), ("b", [6])]}
+    for i in range(10):
+        entries = [{"id": "a", "tokens": [a[60 + i]], "want": [0] if i % 2 == 0 else []}]
+        rows = [("a", [60 + i])] if i % 2 == 0 else []
+        if i < 2:
+            entries.append({"id": "b", "tokens": [b[7 + i]], "want": [0]})
+            rows.append(("b", [7 + i]))
+        end = (["b"] if i == 1 else []) + (["a"] if i == 9 else [])
+        steps.append({"step": i + 1, "entries": entries, "end": end})
+        expect[i + 1] = rows
+    out = tempfile.mkdtemp()
+    root = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..")
+    proc = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", folder,
+                           "--dtype", dtype, "--out", out, "--max-tokens", "128"],
+                          input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True,
+                          text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(11)]
+    for step, rows in expect.items():
+        path = os.path.join(out, f"{step}.f32")
+        if not rows:
+            assert not os.path.exists(path)
+            continue
+        got = torch.from_numpy(np.fromfile(path, dtype="<f4").reshape(-1, cfg["vocab"]))
+        want = torch.cat([plain[r][places] for r, places in rows])
+        _close(got, want, dtype)

@@ -246,6 +246,28 @@ __device__ __forceinline__ void store_chunk(const GemmArgs& a, const uint32_t* r
             if (tok < a.M && n_ok)
                 ((float*)a.out)[(size_t)tok * a.ldo + n] = old[j] + __uint_as_float(r[j]) + bias;
         }
+    } else if (a.out_dtype == MF_DTYPE_BF16 && a.epi != EPI_PARTIAL && (a.N & 1) == 0 && (a.ldo & 1) == 0 &&
+               ((uintptr_t)a.out & 3) == 0) {
+        // bfloat16 out: lanes come in pairs (columns n, n + 1).  They swap halves (one shuffle per two
+        // tokens); the even lane then writes both columns of the even tokens and the odd lane of
+        // the odd ones, four bytes a store instead of two.
+        const bool even = (lane & 1) == 0;
+        __nv_bfloat16* o = (__nv_bfloat16*)a.out + (size_t)(tok0 + (even ? 0 : 1)) * a.ldo + (n & ~1);
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) {
+            float v0 = __uint_as_float(r[2 * jj]) + bias, v1 = __uint_as_float(r[2 * jj + 1]) + bias;
+            if (a.epi == EPI_XIELU) {
+                v0 = v0 > 0.0f ? fmaf(a.act_p * v0, v0, 0.5f * v0) : fmaf(a.act_n, (__expf(v0) - 1.0f) - v0, 0.5f * v0);
+                v1 = v1 > 0.0f ? fmaf(a.act_p * v1, v1, 0.5f * v1) : fmaf(a.act_n, (__expf(v1) - 1.0f) - v1, 0.5f * v1);
+            }
+            const float keep = even ? v0 : v1, send = even ? v1 : v0;
+            const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
+            const int tok = tok0 + 2 * jj + (even ? 0 : 1);
+            if (tok < a.M && n_ok) {
+                const __nv_bfloat162 pair = even ? __floats2bfloat162_rn(keep, recv) : __floats2bfloat162_rn(recv, keep);
+                *reinterpret_cast<__nv_bfloat162*>(o + (size_t)(2 * jj) * a.ldo) = pair;
+            }
+        }
     } else {
 #pragma unroll
         for (int j = 0; j < 16; ++j) {

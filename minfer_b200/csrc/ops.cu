@@ -874,6 +874,81 @@ __global__ void norm_shift_kernel(float* x, const float* __restrict__ partial, i
     }
 }
 
+// the form for prompts: float4 accesses, the row and the row above (or the state) kept in
+// registers, one pass over memory; widths that are multiples of 4 up to 8 * blockDim
+template <typename TO>
+__global__ void __launch_bounds__(1024)
+norm_shift_vec_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                      const float* __restrict__ shift, const int* __restrict__ positions,
+                      const int* __restrict__ token_row, const int* __restrict__ cu_seqlens,
+                      const int* __restrict__ slots, float* __restrict__ state,
+                      TO* __restrict__ y, int width, float eps) {
+    pdl_launch_dependents();
+    __shared__ float scratch[33];
+    const int t = blockIdx.x;
+    const int b = token_row[t];
+    const int pos = positions[t];
+    const bool first = t == cu_seqlens[b];
+    const bool last = t == cu_seqlens[b + 1] - 1;
+    float4* st = reinterpret_cast<float4*>(state + (size_t)slots[b] * width);
+    const int nv = width >> 2;
+    float4 g[2], sh[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < nv) {
+            g[j] = reinterpret_cast<const float4*>(w)[i];
+            sh[j] = reinterpret_cast<const float4*>(shift)[i];
+        }
+    }
+    pdl_wait();
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)t * width);
+    const float4* xp = xr - nv;                         // the row above (used unless first)
+    float4 row[2], prev[2];
+    float ss = 0.0f, sp = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < nv) {
+            const float4 v = xr[i];
+            row[j] = v;
+            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss);
+            ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+            if (!first) {
+                const float4 u = xp[i];
+                prev[j] = u;
+                sp = fmaf(u.x, u.x, sp); sp = fmaf(u.y, u.y, sp);
+                sp = fmaf(u.z, u.z, sp); sp = fmaf(u.w, u.w, sp);
+            } else {
+                prev[j] = pos > 0 ? st[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+    float scale_p = 1.0f;
+    if (!first) {
+        sp = block_sum(sp, scratch);
+        scale_p = 1.0f / sqrtf(sp / (float)width + eps);
+    }
+    TO* yr = y + (size_t)t * width;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < nv) {
+            const float4 v = row[j], u = prev[j], gg = g[j], s4 = sh[j];
+            const float n0 = v.x * scale * gg.x, n1 = v.y * scale * gg.y;
+            const float n2 = v.z * scale * gg.z, n3 = v.w * scale * gg.w;
+            // the state already holds normed values; a row above is normed here
+            const float b0 = first ? u.x : u.x * scale_p * gg.x, b1 = first ? u.y : u.y * scale_p * gg.y;
+            const float b2 = first ? u.z : u.z * scale_p * gg.z, b3 = first ? u.w : u.w * scale_p * gg.w;
+            Pack4<TO>::store(yr + 4 * i, n0 + (b0 - n0) * s4.x, n1 + (b1 - n1) * s4.y,
+                             n2 + (b2 - n2) * s4.z, n3 + (b3 - n3) * s4.w);
+            if (first && last) st[i] = make_float4(n0, n1, n2, n3);
+        }
+    }
+}
+
 __global__ void norm_shift_save_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                        const int* __restrict__ cu_seqlens,
                                        const int* __restrict__ slots, float* __restrict__ state,
@@ -908,6 +983,22 @@ extern "C" int mf_norm_shift(float* x, const float* partial, int n_partials, con
     // the block size is a function of the width only, so a row's sum never depends on the batch
     int threads = 32;
     while (threads < 512 && threads * 4 < width) threads <<= 1;
+    if (n_partials == 0 && (width & 3) == 0 && width <= 8192 && ((uintptr_t)x & 15) == 0 &&
+        ((uintptr_t)state & 15) == 0 && ((uintptr_t)y & 15) == 0 &&
+        (out_dtype == MF_DTYPE_F32 || out_dtype == MF_DTYPE_BF16) && multi) {
+        int vt = 32;
+        while (vt < 1024 && vt * 8 < width) vt <<= 1;
+        if (out_dtype == MF_DTYPE_F32)
+            mf_launch(norm_shift_vec_kernel<float>, dim3(n_tokens), dim3(vt), 0, stream, (const float*)x, w,
+                      shift, positions, token_row, cu_seqlens, slots, state, (float*)y, width, eps);
+        else
+            mf_launch(norm_shift_vec_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(vt), 0, stream,
+                      (const float*)x, w, shift, positions, token_row, cu_seqlens, slots, state,
+                      (__nv_bfloat16*)y, width, eps);
+        mf_launch(norm_shift_save_kernel, dim3(n_rows), dim3(threads), 0, stream, (const float*)x, w,
+                  cu_seqlens, slots, state, width, eps);
+        return MF_LAUNCH_CHECK();
+    }
 #define MF_NORM_SHIFT(TO, SPLITS) \
     mf_launch(norm_shift_kernel<TO, SPLITS>, dim3(n_tokens), dim3(threads), 0, stream, x, partial, \
               n_partials, bias, n_tokens, w, shift, positions, token_row, cu_seqlens, slots, state, \

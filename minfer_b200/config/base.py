@@ -64,6 +64,9 @@ class LayerCall:
     layer: int
     cache: int
     writes_cache: bool = True
+    # this call is the first of pass number ``pass_start`` of a layer loop: right before it the
+    # plan's ``pass_injection`` part adds to the residual stream (None: nothing happens)
+    pass_start: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -90,6 +93,9 @@ class ModelPlan:
     after_embedding: Optional[PartSpec] = None
     on_logits: Optional[PartSpec] = None
     model_part_prefix: str = ""
+    # a part of role "model" with ``add(h, ctx, pass_index, embedding_output)``, run before every
+    # call of the run order that names a ``pass_start``
+    pass_injection: Optional[PartSpec] = None
 
     def validate(self) -> None:
         if self.vocab_size <= 0 or self.hidden_size <= 0:
@@ -105,6 +111,8 @@ class ModelPlan:
                     f"schedule[{i}] names layer {call.layer}, but there are {len(self.layers)} layers")
             if call.cache < 0:
                 raise ConfigError(f"schedule[{i}] has a negative cache entry {call.cache}")
+            if call.pass_start is not None and self.pass_injection is None:
+                raise ConfigError(f"schedule[{i}] starts a pass, but the plan has no pass_injection part")
             if call.writes_cache:
                 if call.cache in writers:
                     raise ConfigError(
@@ -125,6 +133,20 @@ class ModelPlan:
 def default_schedule(n_layers: int) -> list[LayerCall]:
     """Every layer once, in order, each with a cache entry of its own."""
     return [LayerCall(layer=i, cache=i) for i in range(n_layers)]
+
+
+def looped_schedule(n_layers: int, start: int, stop: int, times: int) -> list[LayerCall]:
+    """Layers ``start`` .. ``stop - 1`` run ``times`` times in a row with the same weights, the
+    others once; every run has a cache entry (and state) of its own, and the first run of each
+    pass is marked as its start."""
+    if not 0 <= start < stop <= n_layers or times < 1:
+        raise ConfigError(f"a loop over layers [{start}, {stop}) x {times} does not fit {n_layers} layers")
+    order = [(i, None) for i in range(start)]
+    for t in range(times):
+        order += [(i, t if i == start else None) for i in range(start, stop)]
+    order += [(i, None) for i in range(stop, n_layers)]
+    return [LayerCall(layer=layer, cache=entry, pass_start=mark)
+            for entry, (layer, mark) in enumerate(order)]
 
 
 # ---------------------------------------------------------------------------------------

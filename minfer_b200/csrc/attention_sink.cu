@@ -9,6 +9,9 @@
 //                                                               position 0 of the sequence)
 //     w_ij = exp(s_ij) / (sink + sum over visible j' of exp(s_ij'))       (sink is 0 or 1: a key
 //                                                               of score 0 that has no value)
+// Two further changes of the score, both optional: a soft cap, s <- cap * tanh(s / cap), applied
+// to (q . k) * scale before the bias (cap > 0), and a learned score of the sink per head
+// (sink_logit[h] instead of 0: the denominator holds exp(sink_logit[h]) once).
 //     o_i = sum_j w_ij v_j
 // Keys have `hd` elements a head, values `vd`; the two differ freely.  Scores, the bias, the
 // running maximum and sum, and the weighted sum are float32.
@@ -26,6 +29,7 @@
 
 #define SA_WARPS 4
 #define SA_MAX_D 256
+#define SA_GEN_MAX_D 640      // the generic kernel alone takes keys and values this wide
 
 // ------------------------------------------------------------------------------------------
 // q and k to unit root mean square per head, cache write
@@ -200,6 +204,8 @@ struct SinkArgs {
     int rows, n_heads, n_kv, hd, vd;
     int window, chunk, sink;
     float scale;
+    const float* sink_logit;  // [n_heads] score of the sink, or nullptr for 0
+    float softcap;            // > 0: s <- softcap * tanh(s / softcap) before the bias
 };
 
 // first visible key of a query at `pos`
@@ -231,10 +237,11 @@ template <> struct Vec16<__nv_bfloat16> {
 };
 
 // VEC: hd is a multiple of the 16-byte vector (rows of keys then start on 16-byte boundaries)
-template <typename T, bool PAGED, bool VEC>
+// NACC: 32-element groups of a value vector a lane accumulates (values up to 32 * NACC wide)
+template <typename T, bool PAGED, bool VEC, int NACC>
 __global__ void __launch_bounds__(SA_WARPS * 32) sink_attention_generic_kernel(SinkArgs a) {
     pdl_launch_dependents();
-    __shared__ float q_s[SA_WARPS][SA_MAX_D];
+    __shared__ float q_s[SA_WARPS][SA_GEN_MAX_D];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const long long item = (long long)blockIdx.x * SA_WARPS + warp;
     if (item >= (long long)a.rows * a.n_heads) return;      // no block-wide barrier below
@@ -248,6 +255,8 @@ __global__ void __launch_bounds__(SA_WARPS * 32) sink_attention_generic_kernel(S
     const int hi = pos + 1;
     const float r1 = a.r1 ? a.r1[head] : 0.0f;
     const float r2 = a.r1 ? a.r2[head] : 0.0f;
+    const float sink_score = (a.sink && a.sink_logit) ? a.sink_logit[head] : 0.0f;
+    const float cap = a.softcap, inv_cap = a.softcap > 0.0f ? 1.0f / a.softcap : 0.0f;
     const long long packed0 = PAGED ? 0 : (long long)a.cu_seqlens[b];
     pdl_wait();
 
@@ -257,11 +266,11 @@ __global__ void __launch_bounds__(SA_WARPS * 32) sink_attention_generic_kernel(S
 
     const T* kbase = (const T*)a.k;
     const T* vbase = (const T*)a.v;
-    // the sink is a key of score 0 without a value: it starts the running maximum and sum
-    float m = a.sink ? 0.0f : -INFINITY, l = a.sink ? 1.0f : 0.0f;
-    float acc[SA_MAX_D / 32];
+    // the sink is a key without a value: its score starts the running maximum and sum
+    float m = a.sink ? sink_score : -INFINITY, l = a.sink ? 1.0f : 0.0f;
+    float acc[NACC];
 #pragma unroll
-    for (int i = 0; i < SA_MAX_D / 32; ++i) acc[i] = 0.0f;
+    for (int i = 0; i < NACC; ++i) acc[i] = 0.0f;
 
     for (int j0 = lo; j0 < hi; j0 += 32) {
         const int j = j0 + lane;
@@ -291,6 +300,7 @@ __global__ void __launch_bounds__(SA_WARPS * 32) sink_attention_generic_kernel(S
                 for (int d = 0; d < hd; ++d) dot = fmaf(q_s[warp][d], to_f32(kr[d]), dot);
             }
             s = dot;
+            if (cap > 0.0f) s = cap * tanhf(s * inv_cap);
             if (a.r1) s -= r1 * log1pf(r2 * (float)(pos - j));
         }
         const float m_new = fmaxf(m, warp_max(s));
@@ -299,14 +309,14 @@ __global__ void __launch_bounds__(SA_WARPS * 32) sink_attention_generic_kernel(S
         l = l * corr + warp_sum(p);
         m = m_new;
 #pragma unroll
-        for (int i = 0; i < SA_MAX_D / 32; ++i) acc[i] *= corr;
+        for (int i = 0; i < NACC; ++i) acc[i] *= corr;
         const int n_here = min(32, hi - j0);
         for (int jj = 0; jj < n_here; ++jj) {
             const float pj = __shfl_sync(0xffffffffu, p, jj);
             const long long vrow = __shfl_sync(0xffffffffu, krow, jj);
             const T* vr = vbase + vrow * vd;
 #pragma unroll
-            for (int i = 0; i < SA_MAX_D / 32; ++i) {
+            for (int i = 0; i < NACC; ++i) {
                 const int d = lane + 32 * i;
                 if (d < vd) acc[i] = fmaf(pj, to_f32(vr[d]), acc[i]);
             }
@@ -315,7 +325,7 @@ __global__ void __launch_bounds__(SA_WARPS * 32) sink_attention_generic_kernel(S
     T* o = (T*)a.out + ((size_t)row * a.n_heads + head) * vd;
     const float inv = 1.0f / l;
 #pragma unroll
-    for (int i = 0; i < SA_MAX_D / 32; ++i) {
+    for (int i = 0; i < NACC; ++i) {
         const int d = lane + 32 * i;
         if (d < vd) o[d] = from_f32<T>(acc[i] * inv);
     }
@@ -323,9 +333,9 @@ __global__ void __launch_bounds__(SA_WARPS * 32) sink_attention_generic_kernel(S
 
 static int sink_check(const SinkArgs& a, int dtype) {
     if (dtype != MF_DTYPE_F32 && dtype != MF_DTYPE_BF16) return MF_ERR_UNSUPPORTED;
-    if (a.hd < 1 || a.hd > SA_MAX_D || a.vd < 1 || a.vd > SA_MAX_D) return MF_ERR_UNSUPPORTED;
+    if (a.hd < 1 || a.hd > SA_GEN_MAX_D || a.vd < 1 || a.vd > SA_GEN_MAX_D) return MF_ERR_UNSUPPORTED;
     if (a.n_kv < 1 || a.n_heads % a.n_kv != 0) return MF_ERR_ARGUMENT;
-    if (a.window < 0 || a.chunk < 0) return MF_ERR_ARGUMENT;
+    if (a.window < 0 || a.chunk < 0 || a.softcap < 0.0f) return MF_ERR_ARGUMENT;
     return 0;
 }
 
@@ -334,13 +344,19 @@ static int sink_generic_launch(const SinkArgs& a, int dtype, cudaStream_t stream
     if (a.rows <= 0) return 0;
     const long long items = (long long)a.rows * a.n_heads;
     dim3 grid((unsigned)((items + SA_WARPS - 1) / SA_WARPS)), block(SA_WARPS * 32);
+#define MF_SINK_GEN(T, VEC) \
+    do { \
+        if (a.vd <= SA_MAX_D) mf_launch(sink_attention_generic_kernel<T, PAGED, VEC, SA_MAX_D / 32>, grid, block, 0, stream, a); \
+        else mf_launch(sink_attention_generic_kernel<T, PAGED, VEC, SA_GEN_MAX_D / 32>, grid, block, 0, stream, a); \
+    } while (0)
     if (dtype == MF_DTYPE_F32) {
-        if (a.hd % 4 == 0) mf_launch(sink_attention_generic_kernel<float, PAGED, true>, grid, block, 0, stream, a);
-        else mf_launch(sink_attention_generic_kernel<float, PAGED, false>, grid, block, 0, stream, a);
+        if (a.hd % 4 == 0) MF_SINK_GEN(float, true);
+        else MF_SINK_GEN(float, false);
     } else {
-        if (a.hd % 8 == 0) mf_launch(sink_attention_generic_kernel<__nv_bfloat16, PAGED, true>, grid, block, 0, stream, a);
-        else mf_launch(sink_attention_generic_kernel<__nv_bfloat16, PAGED, false>, grid, block, 0, stream, a);
+        if (a.hd % 8 == 0) MF_SINK_GEN(__nv_bfloat16, true);
+        else MF_SINK_GEN(__nv_bfloat16, false);
     }
+#undef MF_SINK_GEN
     return MF_LAUNCH_CHECK();
 }
 
@@ -348,12 +364,13 @@ static SinkArgs sink_args(const void* q, const void* k, const void* v, const int
                           const int* row_pos, const int* cu_seqlens, const int* page_table,
                           int table_stride, int ring, void* out, const float* r1, const float* r2,
                           int rows, int n_heads, int n_kv, int hd, int vd, int window, int chunk,
-                          int sink, float scale) {
+                          int sink, float scale, const float* sink_logit, float softcap) {
     SinkArgs a;
     a.q = q; a.k = k; a.v = v; a.row_seq = row_seq; a.row_pos = row_pos; a.cu_seqlens = cu_seqlens;
     a.page_table = page_table; a.table_stride = table_stride; a.ring = ring; a.out = out;
     a.r1 = r1; a.r2 = r2; a.rows = rows; a.n_heads = n_heads; a.n_kv = n_kv; a.hd = hd; a.vd = vd;
     a.window = window; a.chunk = chunk; a.sink = sink ? 1 : 0; a.scale = scale;
+    a.sink_logit = sink_logit; a.softcap = softcap;
     return a;
 }
 
@@ -364,9 +381,10 @@ extern "C" int mf_sink_attention_packed(const void* q, const void* k, const void
                                         const int* cu_seqlens, void* out, const float* r1,
                                         const float* r2, int rows, int n_heads, int n_kv, int hd,
                                         int vd, int window, int chunk, int sink, float scale,
+                                        const float* sink_logit, float softcap,
                                         int dtype, cudaStream_t stream) {
     SinkArgs a = sink_args(q, k, v, row_seq, row_pos, cu_seqlens, nullptr, 0, 0, out, r1, r2, rows,
-                           n_heads, n_kv, hd, vd, window, chunk, sink, scale);
+                           n_heads, n_kv, hd, vd, window, chunk, sink, scale, sink_logit, softcap);
     const int bad = sink_check(a, dtype);
     if (bad) return bad;
     return sink_generic_launch<false>(a, dtype, stream);
@@ -378,11 +396,12 @@ extern "C" int mf_sink_attention_paged(const void* q, const void* k_cache, const
                                        const int* page_table, int table_stride, int ring,
                                        void* out, const float* r1, const float* r2, int rows,
                                        int n_heads, int n_kv, int hd, int vd, int window,
-                                       int chunk, int sink, float scale, int dtype,
+                                       int chunk, int sink, float scale,
+                                       const float* sink_logit, float softcap, int dtype,
                                        cudaStream_t stream) {
     SinkArgs a = sink_args(q, k_cache, v_cache, row_seq, row_pos, nullptr, page_table,
                            table_stride, ring, out, r1, r2, rows, n_heads, n_kv, hd, vd, window,
-                           chunk, sink, scale);
+                           chunk, sink, scale, sink_logit, softcap);
     const int bad = sink_check(a, dtype);
     if (bad) return bad;
     if (page_table == nullptr) return MF_ERR_ARGUMENT;

@@ -44,7 +44,10 @@
 
 #define EPI_STORE 0           // out = acc + bias          (float32 or bfloat16)
 #define EPI_ACCUM 1           // out += acc + bias         (float32)
-#define EPI_SWIGLU 2          // rows of W interleaved gate,up: out[j] = silu(g) * u (bfloat16)
+#define EPI_SWIGLU 2          // rows of W interleaved gate,up: out[j] = act(g) * u (bfloat16); act is
+                              // silu, or the tanh form of gelu when the caller's epilogue code
+                              // carries EPI_GATE_GELU_TANH in its second byte
+#define EPI_GATE_GELU_TANH 1
 #define EPI_PARTIAL 3         // ws[split][token][n] = acc (float32)
 #define EPI_XIELU 4           // out = f(acc + bias), f(z) = act_p z^2 + z/2 (z > 0),
                               // act_n (exp(z) - 1 - z) + z/2 (z <= 0)   (float32 or bfloat16)
@@ -74,6 +77,7 @@ struct GemmArgs {
     float* prep_ssq;
     long long ldp;            // elements between consecutive tokens of prep_x
     float act_p, act_n;       // EPI_XIELU: the two coefficients of the activation
+    int gate_act;             // EPI_SWIGLU: 0 silu, EPI_GATE_GELU_TANH
 };
 
 // an epilogue that is not linear in the accumulator cannot run on a K split's partial sums
@@ -218,8 +222,15 @@ __device__ __forceinline__ void store_chunk(const GemmArgs& a, const uint32_t* r
             const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
             const float g = even ? keep : recv, u = even ? recv : keep;
             const int tok = tok0 + 2 * jj + (even ? 0 : 1);
-            if (tok < a.M && n_ok)
-                o[(size_t)(2 * jj) * a.ldo] = __float2bfloat16_rn(__fdividef(g * u, 1.0f + __expf(-g)));
+            float y;
+            if (a.gate_act == EPI_GATE_GELU_TANH) {
+                // 0.5 g (1 + tanh(c (g + 0.044715 g^3))) = g / (1 + exp(-2 c (g + 0.044715 g^3)))
+                const float z = 1.5957691216057308f * fmaf(0.044715f * g, g * g, g);
+                y = __fdividef(g * u, 1.0f + __expf(-z));
+            } else {
+                y = __fdividef(g * u, 1.0f + __expf(-g));
+            }
+            if (tok < a.M && n_ok) o[(size_t)(2 * jj) * a.ldo] = __float2bfloat16_rn(y);
         }
     } else if (a.epi == EPI_ACCUM && a.bias == nullptr) {
         // out += acc as a reduction at the memory side: nothing comes back, so a chunk does not
@@ -1162,6 +1173,7 @@ extern "C" int mf_gemm_pair_plan(int M, int N, int K, int* token_tile, int* dual
 // How a product of these sizes is cut: the token tile and the number of K splits.  A
 // function of the sizes only (never of the data), so results are reproducible.
 extern "C" int mf_gemm_tc_plan(int M, int N, int K, int epi, int* token_tile, int* splits) {
+    epi &= 0xff;                         // (the second byte names a gate's activation)
     // many tokens: 128-token tiles with three stages, so that two CTAs share an SM and one's
     // epilogue overlaps the other's main loop (measured faster than 256-token tiles with one
     // CTA per SM for K = 3584: 958 against 847 TFLOP/s)
@@ -1216,6 +1228,7 @@ struct FusedNorm {
     float act_p = 0.0f, act_n = 0.0f;   // EPI_XIELU
 };
 
+
 static int pair_mode_on() {
     static int pair_mode = -1;            // MINFER_B200_GEMM_PAIR=0 keeps the one-CTA kernel
     if (pair_mode < 0) { const char* ev = getenv("MINFER_B200_GEMM_PAIR"); pair_mode = ev ? atoi(ev) : 1; }
@@ -1244,6 +1257,10 @@ static int gemm_tc_impl(const void* x, long long ldx, const void* w, long long l
                         const float* bias, void* out, long long ldo, int out_dtype, int M, int N,
                         int K, int epi, float* workspace, int* deferred, unsigned* status,
                         const FusedNorm* f, cudaStream_t stream) {
+    // the second byte of the epilogue code names the gate's activation (EPI_SWIGLU only)
+    const int gate_act = (epi >> 8) & 0xff;
+    epi &= 0xff;
+    if (gate_act != 0 && (epi != EPI_SWIGLU || gate_act != EPI_GATE_GELU_TANH)) return MF_ERR_ARGUMENT;
     if (deferred) *deferred = 0;
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0) return MF_ERR_UNSUPPORTED;
@@ -1263,6 +1280,7 @@ static int gemm_tc_impl(const void* x, long long ldx, const void* w, long long l
     GemmArgs a = {};
     a.out = out; a.partial = nullptr; a.bias = bias; a.status = status; a.ldo = ldo;
     a.M = M; a.N = N; a.K = K; a.out_dtype = out_dtype; a.kblocks_per_split = 0; a.epi = epi;
+    a.gate_act = gate_act;
     if (f != nullptr) {
         a.row_ssq = f->row_ssq; a.ssq_parts = f->ssq_parts; a.ssq_width = f->ssq_width; a.ssq_eps = f->ssq_eps;
         a.prep_x = f->prep_x; a.ldp = f->ldp; a.prep_g = f->prep_g; a.prep_ssq = f->prep_ssq;

@@ -1,0 +1,253 @@
+// What attention mixers do between their input projection and the attention itself, for layouts
+// the fused rotary kernel does not take, and the small per-head products of latent attention.
+//
+//   qk_prepare     One block per token.  From the projection's float32 row it takes a query
+//                  segment (n_heads heads of qw) and a key segment (n_kv heads of kw), optionally
+//                  RMS-norms the first q_norm_n / k_norm_n elements of each segment AS A WHOLE
+//                  (all heads at once: x / sqrt(mean(x^2) + eps) * weight), rotates `rot_dims`
+//                  dimensions of every head starting at q_rot_off / k_rot_off (pairs (i, i + R/2)
+//                  or (2i, 2i + 1), angle position * inv_freq[i] formed in float64, cosine and
+//                  sine times `rot_mag`), and writes q, the step's k and v, and the cache's pages.
+//                  Values are a segment of their own (n_kv heads of vw) or, with v_from_k, the
+//                  first vw elements of each prepared key head (a latent shared by both).
+//   head_linear    y[t][h][j] = sum_d W[h][j][d] x[t][h][x_off + d] for every head h, optionally
+//                  times sigmoid(gate[t][h * J + j]), optionally followed by a copy of `tail`
+//                  elements x[t][h][x_tail_off ..] behind the J outputs.  float32 accumulation.
+#include "common.cuh"
+
+struct PrepArgs {
+    const float* proj;        // [tokens][in_width]
+    long long in_width;
+    const int* positions;
+    const int* token_row;
+    const int* seq_end;
+    const double* inv_freq;   // [rot_dims / 2] or null
+    const float* q_norm_w;    // [q_norm_n] or null
+    const float* k_norm_w;    // [k_norm_n] or null
+    void* q_out;              // [tokens][n_heads][qw]
+    void* k_out;              // [tokens][n_kv][kw] or null
+    void* v_out;              // [tokens][n_kv][vw] or null
+    void* k_cache;            // [pages][n_kv][64][kw] or null
+    void* v_cache;            // [pages][n_kv][64][vw] or null
+    const int* page_table;
+    int table_stride, ring;
+    int q_off, n_heads, qw, q_norm_n, q_rot_off;
+    int k_off, n_kv, kw, k_norm_n, k_rot_off;
+    int v_off, vw, v_from_k;
+    int rot_dims, rot_style;  // style 0: pairs (i, i + R/2); 1: pairs (2i, 2i + 1)
+    float rot_mag, eps;
+    unsigned* status;
+};
+
+// element d of a head after norm and rotation; `seg` points at the segment's first element,
+// `e` = head * width + d is the element's place in the segment
+__device__ __forceinline__ float prep_value(const float* seg, const float* norm_w, int norm_n,
+                                            float rinv, int width, int d, int e, int rot_off,
+                                            const PrepArgs& a, const float* cs) {
+    auto normed = [&](int at) {
+        const float v = seg[at];
+        return at < norm_n ? v * rinv * norm_w[at] : v;
+    };
+    const float v = normed(e);
+    const int r = d - rot_off;
+    if (a.rot_dims <= 0 || r < 0 || r >= a.rot_dims) return v;
+    const int half = a.rot_dims >> 1;
+    int pair, partner;
+    bool first;
+    if (a.rot_style == 0) {
+        first = r < half;
+        pair = first ? r : r - half;
+        partner = first ? e + half : e - half;
+    } else {
+        first = (r & 1) == 0;
+        pair = r >> 1;
+        partner = first ? e + 1 : e - 1;
+    }
+    const float other = normed(partner);
+    const float c = cs[2 * pair], s = cs[2 * pair + 1];
+    return first ? v * c - other * s : v * c + other * s;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) qk_prepare_kernel(PrepArgs a) {
+    pdl_launch_dependents();
+    extern __shared__ float pr_cs[];                  // [rot_dims / 2][2] cosine, sine
+    __shared__ float scratch[33];
+    const int t = blockIdx.x;
+    const int pos = a.positions[t];
+    const int b = a.token_row[t];
+    for (int i = threadIdx.x; i < (a.rot_dims >> 1); i += blockDim.x) {
+        double ang = (double)pos * a.inv_freq[i];
+        ang -= 6.283185307179586476925286766559 * floor(ang * 0.15915494309189533576888376337251);
+        float s, c;
+        sincosf((float)ang, &s, &c);
+        pr_cs[2 * i] = c * a.rot_mag;
+        pr_cs[2 * i + 1] = s * a.rot_mag;
+    }
+    int page = -1;
+    if (a.k_cache != nullptr) {
+        bool keep = true;
+        int p_eff = pos;
+        if (a.ring > 0) {
+            keep = pos >= a.seq_end[b] - a.ring;
+            p_eff = pos % a.ring;
+        }
+        if (keep) {
+            page = a.page_table[(size_t)b * a.table_stride + (p_eff >> 6)];
+            if (page < 0 && threadIdx.x == 0) atomicOr(a.status, MF_STATUS_BAD_POSITION);
+        }
+    }
+    pdl_wait();
+    const float* row = a.proj + (size_t)t * a.in_width;
+    const float* qs = row + a.q_off;
+    const float* ks = row + a.k_off;
+    float q_rinv = 1.0f, k_rinv = 1.0f;
+    if (a.q_norm_n > 0) {
+        float ss = 0.0f;
+        for (int i = threadIdx.x; i < a.q_norm_n; i += blockDim.x) ss = fmaf(qs[i], qs[i], ss);
+        ss = block_sum(ss, scratch);
+        q_rinv = 1.0f / sqrtf(ss / (float)a.q_norm_n + a.eps);
+    }
+    if (a.k_norm_n > 0) {
+        float ss = 0.0f;
+        for (int i = threadIdx.x; i < a.k_norm_n; i += blockDim.x) ss = fmaf(ks[i], ks[i], ss);
+        ss = block_sum(ss, scratch);
+        k_rinv = 1.0f / sqrtf(ss / (float)a.k_norm_n + a.eps);
+    }
+    __syncthreads();                                  // the cosines and sines are written
+    T* q_out = (T*)a.q_out + (size_t)t * a.n_heads * a.qw;
+    const int nq = a.n_heads * a.qw;
+    for (int e = threadIdx.x; e < nq; e += blockDim.x) {
+        const int d = e % a.qw;
+        q_out[e] = from_f32<T>(prep_value(qs, a.q_norm_w, a.q_norm_n, q_rinv, a.qw, d, e, a.q_rot_off, a, pr_cs));
+    }
+    const int in_page = pos & (MF_PAGE - 1);
+    const int nk = a.n_kv * a.kw;
+    for (int e = threadIdx.x; e < nk; e += blockDim.x) {
+        const int hk = e / a.kw, d = e - hk * a.kw;
+        const T y = from_f32<T>(prep_value(ks, a.k_norm_w, a.k_norm_n, k_rinv, a.kw, d, e, a.k_rot_off, a, pr_cs));
+        if (a.k_out) ((T*)a.k_out)[(size_t)t * nk + e] = y;
+        if (page >= 0)
+            ((T*)a.k_cache)[(((size_t)page * a.n_kv + hk) * MF_PAGE + in_page) * a.kw + d] = y;
+        if (a.v_from_k && d < a.vw) {
+            if (a.v_out) ((T*)a.v_out)[((size_t)t * a.n_kv + hk) * a.vw + d] = y;
+            if (page >= 0)
+                ((T*)a.v_cache)[(((size_t)page * a.n_kv + hk) * MF_PAGE + in_page) * a.vw + d] = y;
+        }
+    }
+    if (!a.v_from_k) {
+        const float* vs = row + a.v_off;
+        const int nv = a.n_kv * a.vw;
+        for (int e = threadIdx.x; e < nv; e += blockDim.x) {
+            const int hk = e / a.vw, d = e - hk * a.vw;
+            const T y = from_f32<T>(vs[e]);
+            if (a.v_out) ((T*)a.v_out)[(size_t)t * nv + e] = y;
+            if (page >= 0)
+                ((T*)a.v_cache)[(((size_t)page * a.n_kv + hk) * MF_PAGE + in_page) * a.vw + d] = y;
+        }
+    }
+}
+
+extern "C" int mf_qk_prepare(const PrepArgs* args, int n_tokens, int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    const PrepArgs a = *args;
+    if (a.rot_dims < 0 || (a.rot_dims & 1) || (a.rot_dims > 0 && a.inv_freq == nullptr)) return MF_ERR_ARGUMENT;
+    if (a.q_rot_off + a.rot_dims > a.qw || a.k_rot_off + a.rot_dims > a.kw) return MF_ERR_ARGUMENT;
+    if (a.q_norm_n > a.n_heads * a.qw || a.k_norm_n > a.n_kv * a.kw) return MF_ERR_ARGUMENT;
+    if ((a.k_cache == nullptr) != (a.v_cache == nullptr)) return MF_ERR_ARGUMENT;
+    if (a.k_cache != nullptr && a.page_table == nullptr) return MF_ERR_ARGUMENT;
+    if (a.v_from_k && a.vw > a.kw) return MF_ERR_ARGUMENT;
+    // a rotated pair must lie wholly inside or wholly outside the normed stretch of its segment
+    const size_t smem = (size_t)(a.rot_dims > 0 ? a.rot_dims : 2) * sizeof(float);
+    if (dtype == MF_DTYPE_F32)
+        mf_launch(qk_prepare_kernel<float>, dim3(n_tokens), dim3(256), smem, stream, a);
+    else if (dtype == MF_DTYPE_BF16)
+        mf_launch(qk_prepare_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(256), smem, stream, a);
+    else
+        return MF_ERR_UNSUPPORTED;
+    return MF_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------------------------------
+// per-head products
+// ------------------------------------------------------------------------------------------
+#define HL_TT 32          // tokens per block
+#define HL_TJ 32          // outputs per block
+#define HL_TD 32          // reduction chunk
+
+struct HeadLinearArgs {
+    const void* x;            // [tokens][x_row] elements; head h starts at h * x_head
+    const void* w;            // [heads][J][D]
+    void* y;                  // [tokens][y_row]; head h starts at h * y_head
+    const float* gate;        // [tokens][gate_row] float32 at column gate_off + h * J + j, or null
+    long long x_row, y_row, gate_row;
+    int x_head, x_off, y_head, gate_off;
+    int n_tokens, heads, J, D;
+    int tail, x_tail_off;     // copy x[t][h][x_tail_off .. + tail) to y[t][h][J ..)
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) head_linear_kernel(HeadLinearArgs a) {
+    pdl_prologue();
+    __shared__ float xs[HL_TT][HL_TD + 1];
+    __shared__ float ws[HL_TJ][HL_TD + 1];
+    const int h = blockIdx.z;
+    const int t0 = blockIdx.x * HL_TT, j0 = blockIdx.y * HL_TJ;
+    const int tid = threadIdx.x;
+    const int tj = tid & 31, tt = tid >> 5;          // outputs j0 + tj, tokens t0 + tt + 8 i
+    const T* x = (const T*)a.x;
+    const T* w = (const T*)a.w + (size_t)h * a.J * a.D;
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int d0 = 0; d0 < a.D; d0 += HL_TD) {
+        for (int i = tid; i < HL_TT * HL_TD; i += 256) {
+            const int r = i >> 5, d = i & 31;
+            const int tok = t0 + r;
+            xs[r][d] = (tok < a.n_tokens && d0 + d < a.D)
+                ? to_f32(x[(size_t)tok * a.x_row + (size_t)h * a.x_head + a.x_off + d0 + d]) : 0.0f;
+            const int j = j0 + r;
+            ws[r][d] = (j < a.J && d0 + d < a.D) ? to_f32(w[(size_t)j * a.D + d0 + d]) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int d = 0; d < HL_TD; ++d) {
+            const float wv = ws[tj][d];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[i] = fmaf(xs[tt + 8 * i][d], wv, acc[i]);
+        }
+        __syncthreads();
+    }
+    const int j = j0 + tj;
+    T* y = (T*)a.y;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int tok = t0 + tt + 8 * i;
+        if (tok < a.n_tokens && j < a.J) {
+            float v = acc[i];
+            if (a.gate) {
+                const float gv = a.gate[(size_t)tok * a.gate_row + a.gate_off + (size_t)h * a.J + j];
+                v *= 1.0f / (1.0f + expf(-gv));
+            }
+            y[(size_t)tok * a.y_row + (size_t)h * a.y_head + j] = from_f32<T>(v);
+        }
+    }
+    if (a.tail > 0 && blockIdx.y == 0) {
+        for (int i = tid; i < HL_TT * a.tail; i += 256) {
+            const int r = i / a.tail, d = i - r * a.tail;
+            const int tok = t0 + r;
+            if (tok < a.n_tokens)
+                y[(size_t)tok * a.y_row + (size_t)h * a.y_head + a.J + d] =
+                    x[(size_t)tok * a.x_row + (size_t)h * a.x_head + a.x_tail_off + d];
+        }
+    }
+}
+
+extern "C" int mf_head_linear(const HeadLinearArgs* args, int dtype, cudaStream_t stream) {
+    const HeadLinearArgs a = *args;
+    if (a.n_tokens <= 0) return 0;
+    if (a.heads < 1 || a.J < 1 || a.D < 1 || a.tail < 0) return MF_ERR_ARGUMENT;
+    dim3 grid((a.n_tokens + HL_TT - 1) / HL_TT, (a.J + HL_TJ - 1) / HL_TJ, a.heads);
+    if (dtype == MF_DTYPE_F32) mf_launch(head_linear_kernel<float>, grid, dim3(256), 0, stream, a);
+    else if (dtype == MF_DTYPE_BF16) mf_launch(head_linear_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, a);
+    else return MF_ERR_UNSUPPORTED;
+    return MF_LAUNCH_CHECK();
+}

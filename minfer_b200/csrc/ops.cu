@@ -655,9 +655,18 @@ extern "C" int mf_rope_kvstore(const float* qkv, int n_partials, const float* bi
 //   layout 0 (gate rows then up rows):   out[t][j] = silu(gu[t][j])  * gu[t][nf + j]
 //   layout 1 (rows alternate gate, up):  out[t][j] = silu(gu[t][2j]) * gu[t][2j + 1]
 // ------------------------------------------------------------------------------------
+// activation of the gate: 0 silu, 1 the tanh form of gelu
+__device__ __forceinline__ float gate_activation(float g, int act) {
+    if (act == 1) {
+        const float inner = 0.7978845608028654f * fmaf(0.044715f * g, g * g, g);
+        return 0.5f * g * (1.0f + tanhf(inner));
+    }
+    return g / (1.0f + expf(-g));
+}
+
 template <typename TI, typename TO>
 __global__ void swiglu_kernel(const TI* __restrict__ gu, TO* __restrict__ out, int nf,
-                              long long total, int interleaved) {
+                              long long total, int interleaved, int act) {
     pdl_prologue();
     for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (long long)gridDim.x * blockDim.x) {
@@ -665,12 +674,13 @@ __global__ void swiglu_kernel(const TI* __restrict__ gu, TO* __restrict__ out, i
         const int j = (int)(idx - t * nf);
         const float g = to_f32(gu[t * 2 * nf + (interleaved ? 2 * j : j)]);
         const float u = to_f32(gu[t * 2 * nf + (interleaved ? 2 * j + 1 : nf + j)]);
-        out[idx] = from_f32<TO>(g / (1.0f + expf(-g)) * u);
+        out[idx] = from_f32<TO>(gate_activation(g, act) * u);
     }
 }
 
 extern "C" int mf_swiglu(const void* gu, int in_dtype, void* out, int out_dtype, int n_rows, int nf,
-                         int interleaved, cudaStream_t stream) {
+                         int interleaved, int act, cudaStream_t stream) {
+    if (act != 0 && act != 1) return MF_ERR_ARGUMENT;
     const long long total = (long long)n_rows * nf;
     if (total <= 0) return 0;
     const int threads = 256;
@@ -678,7 +688,7 @@ extern "C" int mf_swiglu(const void* gu, int in_dtype, void* out, int out_dtype,
     const int blocks = (int)((total + threads - 1) / threads < cap ? (total + threads - 1) / threads : cap);
 #define MF_SWIGLU(TI, TO) \
     mf_launch(swiglu_kernel<TI, TO>, dim3(blocks), dim3(threads), 0, stream, (const TI*)gu, (TO*)out, nf, total, \
-                                                          interleaved)
+                                                          interleaved, act)
     if (in_dtype == MF_DTYPE_F32 && out_dtype == MF_DTYPE_F32) MF_SWIGLU(float, float);
     else if (in_dtype == MF_DTYPE_F32 && out_dtype == MF_DTYPE_BF16) MF_SWIGLU(float, __nv_bfloat16);
     else if (in_dtype == MF_DTYPE_BF16 && out_dtype == MF_DTYPE_BF16)
@@ -1054,5 +1064,59 @@ extern "C" int mf_xielu(const void* in, int in_dtype, void* out, int out_dtype, 
         MF_XIELU(__nv_bfloat16, __nv_bfloat16);
     else return MF_ERR_UNSUPPORTED;
 #undef MF_XIELU
+    return MF_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------------------------
+// soft cap: x <- cap * tanh(x / cap), in place, float32 (logits)
+// ------------------------------------------------------------------------------------
+__global__ void tanh_cap_kernel(float* __restrict__ x, long long n, float cap, float inv_cap) {
+    pdl_prologue();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (long long)gridDim.x * blockDim.x)
+        x[i] = cap * tanhf(x[i] * inv_cap);
+}
+
+extern "C" int mf_tanh_cap(float* x, long long n, float cap, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (!(cap > 0.0f)) return MF_ERR_ARGUMENT;
+    const long long cap_blocks = (long long)mf_sm_count() * 16;
+    const long long want = (n + 255) / 256;
+    mf_launch(tanh_cap_kernel, dim3((unsigned)(want < cap_blocks ? want : cap_blocks)), dim3(256), 0,
+              stream, x, n, cap, 1.0f / cap);
+    return MF_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------------------------
+// h[t][:] += other[t][:] (optional) + vec[:] (optional): what a pass of a layer loop adds to
+// the residual stream before its first layer
+// ------------------------------------------------------------------------------------
+template <typename TV>
+__global__ void add_stream_kernel(float* __restrict__ h, const float* __restrict__ other,
+                                  const TV* __restrict__ vec, long long total, int width) {
+    pdl_prologue();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        float v = h[i];
+        if (other) v += other[i];
+        if (vec) v += to_f32(vec[i % width]);
+        h[i] = v;
+    }
+}
+
+extern "C" int mf_add_stream(float* h, const float* other, const void* vec, int vec_dtype,
+                             int n_rows, int width, cudaStream_t stream) {
+    const long long total = (long long)n_rows * width;
+    if (total <= 0) return 0;
+    const long long cap_blocks = (long long)mf_sm_count() * 16;
+    const long long want = (total + 255) / 256;
+    dim3 grid((unsigned)(want < cap_blocks ? want : cap_blocks));
+    if (vec_dtype == MF_DTYPE_F32)
+        mf_launch(add_stream_kernel<float>, grid, dim3(256), 0, stream, h, other, (const float*)vec, total, width);
+    else if (vec_dtype == MF_DTYPE_BF16)
+        mf_launch(add_stream_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, h, other,
+                  (const __nv_bfloat16*)vec, total, width);
+    else
+        return MF_ERR_UNSUPPORTED;
     return MF_LAUNCH_CHECK();
 }

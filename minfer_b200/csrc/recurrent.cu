@@ -1,0 +1,297 @@
+// Kernels of a selective state-space mixer (Mamba-2 form): short causal convolution with its
+// state, the recurrence with its state, and the gated group norm behind it.
+//
+// The input projection's float32 output `proj` [tokens][in_width] holds, per token,
+//     [ z : inner | x : inner | B : groups * N | C : groups * N | dt : heads ],   inner = heads * P.
+// Tokens are packed row after row (row b: tokens cu_seqlens[b] .. cu_seqlens[b + 1]); a row goes
+// on from what its slot's state holds, so a step may bring any number of tokens per row.
+//
+//   conv_silu         u[t][c] = silu(bias[c] + sum_j taps[c][j] * in[t - (T - 1 - j)][c]) over the
+//                     channels c of x | B | C; inputs before the row's first token come from the
+//                     slot's state (the last T - 1 inputs, oldest first; zeros for a new sequence)
+//   conv_state        the state after the step (a kernel of its own unless every row brings one
+//                     token: a row's first block reads what its last would write)
+//   ssm_scan          per (row, head): dt = softplus(raw + dt_bias), a = exp(-exp(A_log) dt),
+//                     S <- a S + dt B x^T (S is N x P, float32, kept per slot as [P][N]),
+//                     y = S^T C + D x; tokens of a row one after another
+//   gated_group_norm  v = y * silu(z); each of `groups` equal parts of v divided by its root mean
+//                     square (eps inside the root), times a weight
+// All arithmetic is float32.
+#include "common.cuh"
+
+#define RC_MAX_TAPS 8
+
+__device__ __forceinline__ float rc_silu(float v) { return v / (1.0f + expf(-v)); }
+__device__ __forceinline__ float rc_softplus(float v) {
+    return fmaxf(v, 0.0f) + log1pf(expf(-fabsf(v)));
+}
+
+// ------------------------------------------------------------------------------------------
+// convolution
+// ------------------------------------------------------------------------------------------
+// one thread per (token, channel); `single`: every row brings one token and the thread also
+// writes the state
+__global__ void __launch_bounds__(256)
+conv_silu_kernel(const float* __restrict__ proj, long long in_width, int x_off, int channels,
+                 int taps, const float* __restrict__ w, const float* __restrict__ bias,
+                 float* __restrict__ state, const int* __restrict__ token_row,
+                 const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
+                 float* __restrict__ out, long long total, int single) {
+    pdl_launch_dependents();
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int t = (int)(idx / channels), c = (int)(idx - (long long)t * channels);
+    float wt[RC_MAX_TAPS];
+#pragma unroll
+    for (int j = 0; j < RC_MAX_TAPS; ++j) wt[j] = j < taps ? w[(size_t)c * taps + j] : 0.0f;
+    float acc = bias ? bias[c] : 0.0f;
+    const int b = token_row[t];
+    const int i = t - cu_seqlens[b];
+    const int slot = slots[b];
+    pdl_wait();
+    float* st = state + ((size_t)slot * channels + c) * (taps - 1);
+    float in_cur = 0.0f;
+#pragma unroll
+    for (int j = 0; j < RC_MAX_TAPS; ++j) {
+        if (j < taps) {
+            const int s = i - (taps - 1 - j);
+            const float v = s >= 0 ? proj[(size_t)(t - (i - s)) * in_width + x_off + c]
+                                   : st[taps - 1 + s];
+            acc = fmaf(wt[j], v, acc);
+            if (j == taps - 1) in_cur = v;
+        }
+    }
+    out[idx] = rc_silu(acc);
+    if (single && taps > 1) {
+        // this thread alone owns the (slot, channel): shift and append
+        float old[RC_MAX_TAPS];
+#pragma unroll
+        for (int j = 0; j < RC_MAX_TAPS; ++j) old[j] = j < taps - 1 ? st[j] : 0.0f;
+#pragma unroll
+        for (int j = 0; j < RC_MAX_TAPS; ++j)
+            if (j < taps - 1) st[j] = j + 1 < taps - 1 ? old[j + 1] : in_cur;
+    }
+}
+
+// one thread per (row, channel): the state after the row's tokens
+__global__ void __launch_bounds__(256)
+conv_state_kernel(const float* __restrict__ proj, long long in_width, int x_off, int channels,
+                  int taps, float* __restrict__ state, const int* __restrict__ cu_seqlens,
+                  const int* __restrict__ slots, long long total) {
+    pdl_launch_dependents();
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int b = (int)(idx / channels), c = (int)(idx - (long long)b * channels);
+    const int t0 = cu_seqlens[b], n_b = cu_seqlens[b + 1] - t0;
+    const int slot = slots[b];
+    pdl_wait();
+    float* st = state + ((size_t)slot * channels + c) * (taps - 1);
+    float fresh[RC_MAX_TAPS];
+#pragma unroll
+    for (int j = 0; j < RC_MAX_TAPS; ++j) {
+        fresh[j] = 0.0f;
+        if (j < taps - 1) {
+            const int s = n_b - (taps - 1) + j;            // place in the row of the j-th kept input
+            fresh[j] = s >= 0 ? proj[(size_t)(t0 + s) * in_width + x_off + c] : st[j + n_b];
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < RC_MAX_TAPS; ++j)
+        if (j < taps - 1) st[j] = fresh[j];
+}
+
+extern "C" int mf_conv_silu(const float* proj, long long in_width, int x_off, int channels, int taps,
+                            const float* w, const float* bias, float* state, const int* token_row,
+                            const int* cu_seqlens, const int* slots, float* out, int n_tokens,
+                            int n_rows, int single, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (taps < 1 || taps > RC_MAX_TAPS || channels < 1) return MF_ERR_UNSUPPORTED;
+    const long long total = (long long)n_tokens * channels;
+    mf_launch(conv_silu_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, proj,
+              in_width, x_off, channels, taps, w, bias, state, token_row, cu_seqlens, slots, out,
+              total, single);
+    if (!single && taps > 1) {
+        const long long per_row = (long long)n_rows * channels;
+        mf_launch(conv_state_kernel, dim3((unsigned)((per_row + 255) / 256)), dim3(256), 0, stream,
+                  proj, in_width, x_off, channels, taps, state, cu_seqlens, slots, per_row);
+    }
+    return MF_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------------------------------
+// the recurrence
+// ------------------------------------------------------------------------------------------
+// A block owns one head of one row and up to RC_PB of its P columns; thread (p, s) keeps the NREG
+// state elements n = s * NREG + r of column p in registers (RC_NS = 8 threads share a column:
+// their sums for y meet by shuffles).  Tokens come in chunks of RC_TC through shared memory.
+#define RC_NS 8
+#define RC_PB 64
+#define RC_TC 16
+
+struct ScanArgs {
+    const float* u;           // [tokens][channels] conv output: x | B | C
+    const float* proj;        // [tokens][in_width]: dt at column dt_off + head
+    long long in_width;
+    int dt_off, channels;
+    const float* dt_bias;     // [heads]
+    const float* a_log;       // [heads]
+    const float* d_skip;      // [heads]
+    float* state;             // [slots][heads][P][N]
+    const int* cu_seqlens;
+    const int* slots;
+    float* y;                 // [tokens][heads * P]
+    int heads, P, N, groups;
+};
+
+template <int NREG>
+__global__ void __launch_bounds__(RC_PB * RC_NS) ssm_scan_kernel(ScanArgs a) {
+    pdl_launch_dependents();
+    extern __shared__ float rc_smem[];
+    const int b = blockIdx.x, h = blockIdx.y, p0 = blockIdx.z * RC_PB;
+    const int tid = threadIdx.x, s = tid & (RC_NS - 1), pl = tid >> 3;
+    const int p = p0 + pl;
+    const int n_p = min(RC_PB, a.P - p0);
+    const bool p_ok = pl < n_p;
+    const int N = a.N, P = a.P;
+    float* xs = rc_smem;                          // [TC][RC_PB]
+    float* Bs = xs + RC_TC * RC_PB;               // [TC][N]
+    float* Cs = Bs + RC_TC * N;                   // [TC][N]
+    float* dts = Cs + RC_TC * N;                  // [TC]
+    float* das = dts + RC_TC;                     // [TC]
+    const int g = h / (a.heads / a.groups);
+    const float bias = a.dt_bias[h];
+    const float rate = expf(a.a_log[h]);
+    const float dsk = a.d_skip[h];
+    const int t0 = a.cu_seqlens[b], n_b = a.cu_seqlens[b + 1] - t0;
+    const int slot = a.slots[b];
+    const int inner = a.heads * P;
+    pdl_wait();
+    float* st = a.state + (((size_t)slot * a.heads + h) * P + (p_ok ? p : p0)) * N;
+    float S[NREG];
+#pragma unroll
+    for (int r = 0; r < NREG; ++r) {
+        const int n = s * NREG + r;
+        S[r] = (p_ok && n < N) ? st[n] : 0.0f;
+    }
+    for (int c0 = 0; c0 < n_b; c0 += RC_TC) {
+        const int nc = min(RC_TC, n_b - c0);
+        __syncthreads();
+        for (int i = tid; i < nc * n_p; i += blockDim.x) {
+            const int tt = i / n_p, pp = i - tt * n_p;
+            xs[tt * RC_PB + pp] = a.u[(size_t)(t0 + c0 + tt) * a.channels + h * P + p0 + pp];
+        }
+        for (int i = tid; i < nc * N; i += blockDim.x) {
+            const int tt = i / N, n = i - tt * N;
+            const float* row = a.u + (size_t)(t0 + c0 + tt) * a.channels + inner + g * N + n;
+            Bs[tt * N + n] = row[0];
+            Cs[tt * N + n] = row[(size_t)a.groups * N];
+        }
+        if (tid < nc) {
+            const float dt = rc_softplus(a.proj[(size_t)(t0 + c0 + tid) * a.in_width + a.dt_off + h] + bias);
+            dts[tid] = dt;
+            das[tid] = expf(-rate * dt);
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nc; ++tt) {
+            const float xv = p_ok ? xs[tt * RC_PB + pl] : 0.0f;
+            const float da = das[tt], dtx = dts[tt] * xv;
+            const float* Bt = Bs + tt * N + s * NREG;
+            const float* Ct = Cs + tt * N + s * NREG;
+            float acc = 0.0f;
+#pragma unroll
+            for (int r = 0; r < NREG; ++r) {
+                if (s * NREG + r < N) {
+                    S[r] = fmaf(da, S[r], dtx * Bt[r]);
+                    acc = fmaf(S[r], Ct[r], acc);
+                }
+            }
+            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+            if (s == 0 && p_ok)
+                a.y[(size_t)(t0 + c0 + tt) * inner + h * P + p] = fmaf(dsk, xv, acc);
+        }
+    }
+    if (p_ok) {
+#pragma unroll
+        for (int r = 0; r < NREG; ++r) {
+            const int n = s * NREG + r;
+            if (n < N) st[n] = S[r];
+        }
+    }
+}
+
+extern "C" int mf_ssm_scan(const float* u, const float* proj, long long in_width, int dt_off,
+                           int channels, const float* dt_bias, const float* a_log,
+                           const float* d_skip, float* state, const int* cu_seqlens,
+                           const int* slots, float* y, int n_rows, int heads, int P, int N,
+                           int groups, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (heads < 1 || P < 1 || N < 1 || N > RC_NS * 32) return MF_ERR_UNSUPPORTED;
+    if (groups < 1 || heads % groups != 0) return MF_ERR_ARGUMENT;
+    ScanArgs a;
+    a.u = u; a.proj = proj; a.in_width = in_width; a.dt_off = dt_off; a.channels = channels;
+    a.dt_bias = dt_bias; a.a_log = a_log; a.d_skip = d_skip; a.state = state;
+    a.cu_seqlens = cu_seqlens; a.slots = slots; a.y = y; a.heads = heads; a.P = P; a.N = N;
+    a.groups = groups;
+    const int pb = P < RC_PB ? P : RC_PB;
+    dim3 grid(n_rows, heads, (P + RC_PB - 1) / RC_PB), block(((pb * RC_NS + 31) / 32) * 32);
+    const size_t smem = (size_t)(RC_TC * (RC_PB + 2 * N + 2)) * sizeof(float);
+    const int nreg = (N + RC_NS - 1) / RC_NS;
+#define MF_SCAN(NR) \
+    do { \
+        if (smem > 48 * 1024) \
+            cudaFuncSetAttribute(ssm_scan_kernel<NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        mf_launch(ssm_scan_kernel<NR>, grid, block, smem, stream, a); \
+    } while (0)
+    if (nreg <= 2) MF_SCAN(2);
+    else if (nreg <= 4) MF_SCAN(4);
+    else if (nreg <= 8) MF_SCAN(8);
+    else if (nreg <= 16) MF_SCAN(16);
+    else MF_SCAN(32);
+#undef MF_SCAN
+    return MF_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------------------------------
+// gate, then group norm
+// ------------------------------------------------------------------------------------------
+template <typename TO>
+__global__ void __launch_bounds__(256)
+gated_group_norm_kernel(const float* __restrict__ y, const float* __restrict__ proj,
+                        long long in_width, int z_off, const float* __restrict__ w,
+                        TO* __restrict__ out, int inner, int groups, float eps) {
+    pdl_prologue();
+    __shared__ float scratch[33];
+    const int t = blockIdx.x, grp = blockIdx.y;
+    const int gs = inner / groups;
+    const float* yr = y + (size_t)t * inner + grp * gs;
+    const float* zr = proj + (size_t)t * in_width + z_off + grp * gs;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < gs; i += blockDim.x) {
+        const float v = yr[i] * rc_silu(zr[i]);
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float f = 1.0f / sqrtf(ss / (float)gs + eps);
+    TO* o = out + (size_t)t * inner + grp * gs;
+    for (int i = threadIdx.x; i < gs; i += blockDim.x)
+        o[i] = from_f32<TO>(yr[i] * rc_silu(zr[i]) * f * w[grp * gs + i]);
+}
+
+extern "C" int mf_gated_group_norm(const float* y, const float* proj, long long in_width, int z_off,
+                                   const float* w, void* out, int out_dtype, int n_tokens,
+                                   int inner, int groups, float eps, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (groups < 1 || inner % groups != 0) return MF_ERR_ARGUMENT;
+    dim3 grid(n_tokens, groups);
+    if (out_dtype == MF_DTYPE_F32)
+        mf_launch(gated_group_norm_kernel<float>, grid, dim3(256), 0, stream, y, proj, in_width, z_off,
+                  w, (float*)out, inner, groups, eps);
+    else if (out_dtype == MF_DTYPE_BF16)
+        mf_launch(gated_group_norm_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, y, proj, in_width,
+                  z_off, w, (__nv_bfloat16*)out, inner, groups, eps);
+    else
+        return MF_ERR_UNSUPPORTED;
+    return MF_LAUNCH_CHECK();
+}

@@ -150,6 +150,9 @@ class Engine:
         if not all(getattr(p, "capturable", False) for p in parts):
             self.cuda_graphs = False
         self._graph_pool = None
+        # for inspection: ``layer_tap(i, h)`` is called with the complete residual stream after
+        # entry ``i`` of the run order (steps then run kernel by kernel, never as graphs)
+        self.layer_tap = None
         self.steps_run = 0
         self.h2d_bytes = 0          # bytes of step inputs copied to the device so far
         self.d2h_bytes = 0          # bytes of results read back so far
@@ -222,7 +225,7 @@ class Engine:
         from_start = all(s == 0 for s in starts)
         single = all(c == 1 for c in counts)
         logits = None
-        if (self.cuda_graphs and single and not from_start
+        if (self.cuda_graphs and single and not from_start and self.layer_tap is None
                 and all(list(w) == [0] for w in want)):
             logits = self._graph_step(slots, tokens, starts, None)
             if logits is not None:
@@ -494,7 +497,11 @@ class Engine:
         else:
             K.embed(model.embedding, ctx.token_ids, h, self.status, plan.embedding_scale)
             if model.after_embedding is not None:
-                model.after_embedding.forward_inplace(h, ctx)
+                h = model.after_embedding.forward(h, ctx)
+        # a layer loop adds the embedding output to the stream again before its later passes
+        embedding_output = None
+        if model.pass_injection is not None and model.pass_injection.needs_embedding():
+            embedding_output = h.clone()
         bindings = self._bindings(ctx)
         last = len(plan.schedule) - 1
         n_want = 0 if want_rows is None else want_rows.numel()
@@ -505,6 +512,11 @@ class Engine:
             if not takes_pending:
                 settle_pending(ctx, h)
                 ctx.extras.pop("prepared", None)     # h is complete: the block norms it itself
+            if call.pass_start is not None:
+                # a pass of a layer loop begins: what it adds goes into the complete stream
+                settle_pending(ctx, h)
+                ctx.extras.pop("prepared", None)
+                model.pass_injection.add(h, ctx, call.pass_start, embedding_output)
             # rows of h are dropped between the last mixer and its feed-forward unless all are wanted
             ctx.extras["rows_stay"] = i != last or all_rows
             block.mix(h, ctx, bindings[i])
@@ -523,11 +535,17 @@ class Engine:
             # the norm that reads h after this block's feed-forward: the next block's first, if
             # it can take its input prepared, or the model's last (the head applies the scale)
             if i < last:
-                ctx.extras["next_norm"] = model.blocks[plan.schedule[i + 1].layer].entry_norm()
+                nxt = plan.schedule[i + 1]
+                # (a pass that starts there changes the stream before that norm reads it)
+                ctx.extras["next_norm"] = (model.blocks[nxt.layer].entry_norm()
+                                           if nxt.pass_start is None else None)
             else:
                 ctx.extras["next_norm"] = (model.final_norm if model.head.takes_row_scale()
                                            and model.final_norm.foldable() is not None else None)
             block.feed(h, ctx)
+            if self.layer_tap is not None and (i < last or all_rows):
+                settle_pending(ctx, h)
+                self.layer_tap(i, h)
         prepared = ctx.extras.pop("prepared", None)
         if prepared is not None and prepared.norm is model.final_norm:
             logits = model.head.forward(prepared.x, torch.float32, row_scale=prepared.scale)

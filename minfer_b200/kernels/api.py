@@ -104,7 +104,7 @@ def _sig_ops(lib: ctypes.CDLL) -> None:
                                     [c_void_p, c_void_p])
     lib.mf_add_rmsnorm.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                    c_int, c_int, c_float, c_void_p]
-    lib.mf_swiglu.argtypes = [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+    lib.mf_swiglu.argtypes = [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
     lib.mf_gather_rows.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
     lib.mf_cast.argtypes = [c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p]
     lib.mf_add_rows.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p,
@@ -112,6 +112,8 @@ def _sig_ops(lib: ctypes.CDLL) -> None:
     lib.mf_norm_shift.argtypes = ([c_void_p, c_void_p, c_int] + [c_void_p] * 9 +
                                   [c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
     lib.mf_xielu.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_longlong, c_void_p]
+    lib.mf_tanh_cap.argtypes = [c_void_p, c_longlong, c_float, c_void_p]
+    lib.mf_add_stream.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
 
 
 def _sig_gemm_simt(lib: ctypes.CDLL) -> None:
@@ -130,9 +132,10 @@ def _sig_attention(lib: ctypes.CDLL) -> None:
 def _sig_attention_sink(lib: ctypes.CDLL) -> None:
     lib.mf_unit_norm_kvstore.argtypes = ([c_void_p, c_int] + [c_void_p] * 9 + [c_int] * 7 +
                                          [c_float, c_int, c_int, c_void_p, c_void_p])
-    lib.mf_sink_attention_packed.argtypes = ([c_void_p] * 9 + [c_int] * 8 + [c_float, c_int, c_void_p])
+    lib.mf_sink_attention_packed.argtypes = ([c_void_p] * 9 + [c_int] * 8 +
+                                             [c_float, c_void_p, c_float, c_int, c_void_p])
     lib.mf_sink_attention_paged.argtypes = ([c_void_p] * 6 + [c_int, c_int] + [c_void_p] * 3 +
-                                            [c_int] * 8 + [c_float, c_int, c_void_p])
+                                            [c_int] * 8 + [c_float, c_void_p, c_float, c_int, c_void_p])
 
 
     lib.mf_sink_attention_mma_supported.argtypes = [c_int, c_int]
@@ -191,7 +194,22 @@ def _sig_attention_prefill_tc(lib: ctypes.CDLL) -> None:
                                          [c_float, c_longlong, c_void_p, c_void_p])
 
 
-_SIGNATURES = {"attention_prefill_tc": _sig_attention_prefill_tc,
+def _sig_recurrent(lib: ctypes.CDLL) -> None:
+    lib.mf_conv_silu.argtypes = ([c_void_p, c_longlong, c_int, c_int, c_int] + [c_void_p] * 7 +
+                                 [c_int, c_int, c_int, c_void_p])
+    lib.mf_ssm_scan.argtypes = ([c_void_p, c_void_p, c_longlong, c_int, c_int] + [c_void_p] * 7 +
+                                [c_int] * 5 + [c_void_p])
+    lib.mf_gated_group_norm.argtypes = [c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p,
+                                        c_int, c_int, c_int, c_int, c_float, c_void_p]
+
+
+def _sig_mixer_prep(lib: ctypes.CDLL) -> None:
+    lib.mf_qk_prepare.argtypes = [c_void_p, c_int, c_int, c_void_p]
+    lib.mf_head_linear.argtypes = [c_void_p, c_int, c_void_p]
+
+
+_SIGNATURES = {"attention_prefill_tc": _sig_attention_prefill_tc, "recurrent": _sig_recurrent,
+               "mixer_prep": _sig_mixer_prep,
                "attention_sink": _sig_attention_sink,
                "attention_prefill": _sig_attention_prefill, "gemm_tc": _sig_gemm_tc, "ops": _sig_ops, "gemm_simt": _sig_gemm_simt, "attention": _sig_attention,
                "sampling": _sig_sampling}
@@ -294,15 +312,19 @@ def rope_kvstore(qkv: torch.Tensor, positions: torch.Tensor, token_row: torch.Te
         _stream()), "rope_kvstore")
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> None:
-    """out = silu(gate) * up; ``interleaved``: the columns of ``gate_up`` alternate gate, up
-    instead of all gates first."""
+GATE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False,
+           activation: str = "silu") -> None:
+    """out = act(gate) * up, act the silu or the tanh form of gelu; ``interleaved``: the columns
+    of ``gate_up`` alternate gate, up instead of all gates first."""
     n, nf = out.shape
     if gate_up.shape != (n, 2 * nf):
         raise KernelError("swiglu: shapes do not fit")
     _check(_lib("ops").mf_swiglu(_ptr(gate_up, "gate_up"), dtype_code(gate_up.dtype),
                                  _ptr(out, "out"), dtype_code(out.dtype), n, nf,
-                                 1 if interleaved else 0, _stream()),
+                                 1 if interleaved else 0, GATE_ACTIVATIONS[activation], _stream()),
            "swiglu")
 
 
@@ -360,6 +382,23 @@ def norm_shift(x: torch.Tensor, weight: torch.Tensor, shift: torch.Tensor, eps: 
         1 if multi else 0, _stream()), "norm_shift", 2 if multi else 1)
 
 
+def tanh_cap(x: torch.Tensor, cap: float) -> None:
+    """x <- cap * tanh(x / cap) in place (float32)."""
+    _check(_lib("ops").mf_tanh_cap(_f32(x, "x"), x.numel(), float(cap), _stream()), "tanh_cap")
+
+
+def add_stream(h: torch.Tensor, other: Optional[torch.Tensor], vec: Optional[torch.Tensor]) -> None:
+    """h[t] += other[t] + vec (each optional), float32 rows; ``vec`` [width] in any dtype."""
+    n, width = h.shape
+    if other is not None and other.shape != h.shape:
+        raise KernelError("add_stream: the added rows have another shape")
+    if vec is not None and vec.numel() != width:
+        raise KernelError("add_stream: the added vector has another width")
+    _check(_lib("ops").mf_add_stream(_f32(h, "h"), _f32(other, "other"), _ptr(vec, "vec"),
+                                     dtype_code(vec.dtype) if vec is not None else F32, n, width,
+                                     _stream()), "add_stream")
+
+
 def xielu(x: torch.Tensor, params: torch.Tensor, out: torch.Tensor) -> None:
     """out = softplus(a0) z^2 + z/2 for z > 0, (1/2 + softplus(a1)) (exp(z) - 1 - z) + z/2
     otherwise; ``params`` = (a0, a1) float32 on the device."""
@@ -398,6 +437,13 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
 # matrix product on the tensor cores (bfloat16 x bfloat16, float32 accumulation)
 # ---------------------------------------------------------------------------------------
 EPI_STORE, EPI_ACCUM, EPI_SWIGLU = 0, 1, 2
+# the gated epilogue with the tanh form of gelu on the gate instead of silu (the activation's
+# code rides in the second byte of the epilogue code)
+EPI_GEGLU_TANH = EPI_SWIGLU | (1 << 8)
+
+
+def gated_epilogue(activation: str) -> int:
+    return EPI_SWIGLU | (GATE_ACTIVATIONS[activation] << 8)
 
 
 def gemm_tc_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -459,7 +505,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out:
     n = w.shape[0]
     if w.shape[1] != k:
         raise KernelError(f"gemm: shapes do not fit: x {tuple(x.shape)}, w {tuple(w.shape)}")
-    want_cols = n // 2 if epi == EPI_SWIGLU else n
+    want_cols = n // 2 if (epi & 0xff) == EPI_SWIGLU else n
     if out.shape != (m, want_cols) or out.stride(1) != 1:
         raise KernelError(f"gemm: out has shape {tuple(out.shape)}, expected {(m, want_cols)}")
     if not gemm_tc_supported(x, w):
@@ -467,7 +513,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out:
     if bias is not None and bias.numel() != n:
         raise KernelError("gemm: bias has the wrong length")
     lib = _lib("gemm_tc")
-    need = _gemm_tc_shape(m, n, k, epi)[2]
+    need = _gemm_tc_shape(m, n, k, epi & 0xff)[2]
     ws = torch.empty(need, dtype=torch.float32, device=x.device) if need else None
     _check(lib.mf_gemm_tc(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), _f32(bias, "bias"),
                           out.data_ptr(), out.stride(0), dtype_code(out.dtype), m, n, k, epi,
@@ -541,7 +587,7 @@ def gemm_tc_fused(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]
         raise KernelError(f"gemm: shapes do not fit: x {tuple(x.shape)}, w {tuple(w.shape)}")
     if not gemm_tc_supported(x, w):
         raise KernelError("gemm_tc: operands must be bfloat16 with 16-byte aligned rows")
-    want_cols = n // 2 if epi == EPI_SWIGLU else n
+    want_cols = n // 2 if (epi & 0xff) == EPI_SWIGLU else n
     if out is not None and (out.shape != (m, want_cols) or out.stride(1) != 1):
         raise KernelError(f"gemm: out has shape {tuple(out.shape)}, expected {(m, want_cols)}")
     if bias is not None and bias.numel() != n:
@@ -557,7 +603,7 @@ def gemm_tc_fused(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]
                 or prep_ssq.shape != (parts, m)):
             raise KernelError("gemm: the next norm's tensors have the wrong shapes")
     lib = _lib("gemm_tc")
-    need = _gemm_tc_shape(m, n, k, epi)[2]
+    need = _gemm_tc_shape(m, n, k, epi & 0xff)[2]
     ws = None
     if need and prep_x is None:
         ws = torch.empty(need, dtype=torch.float32, device=x.device)
@@ -735,6 +781,157 @@ def attention_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
 
 
 # ---------------------------------------------------------------------------------------
+# state-space mixer (csrc/recurrent.cu)
+# ---------------------------------------------------------------------------------------
+def conv_silu(proj: torch.Tensor, x_off: int, channels: int, weight: torch.Tensor,
+              bias: Optional[torch.Tensor], state: torch.Tensor, token_row: torch.Tensor,
+              cu_seqlens: torch.Tensor, slots: torch.Tensor, out: torch.Tensor, n_rows: int,
+              single: bool) -> None:
+    """out[t][c] = silu(bias[c] + sum_j weight[c][j] * in[t - (taps - 1 - j)][c]) over the columns
+    x_off .. x_off + channels of ``proj`` (float32 [tokens, width]); inputs before a row's first
+    token come from ``state`` [slots, channels, taps - 1], which then takes the row's last ones."""
+    n = proj.shape[0]
+    taps = weight.shape[1]
+    if (weight.shape[0] != channels or out.shape != (n, channels) or state.shape[1:] != (channels, max(taps - 1, 0))
+            or x_off + channels > proj.shape[1]):
+        raise KernelError("conv_silu: shapes do not fit")
+    _check(_lib("recurrent").mf_conv_silu(
+        _f32(proj, "proj"), proj.shape[1], int(x_off), int(channels), int(taps), _f32(weight, "weight"),
+        _f32(bias, "bias"), _f32(state, "state"), _i32(token_row, "token_row"),
+        _i32(cu_seqlens, "cu_seqlens"), _i32(slots, "slots"), _f32(out, "out"), n, int(n_rows),
+        1 if single else 0, _stream()), "conv_silu", 1 if single or taps < 2 else 2)
+
+
+def ssm_scan(u: torch.Tensor, proj: torch.Tensor, dt_off: int, dt_bias: torch.Tensor,
+             a_log: torch.Tensor, d_skip: torch.Tensor, state: torch.Tensor,
+             cu_seqlens: torch.Tensor, slots: torch.Tensor, y: torch.Tensor, n_rows: int,
+             heads: int, head_dim: int, n_state: int, groups: int) -> None:
+    """The selective recurrence per (row, head), tokens one after another:
+    dt = softplus(proj[t][dt_off + h] + dt_bias[h]); S <- exp(-exp(a_log[h]) dt) S + dt B x^T;
+    y = S^T C + d_skip[h] x, with x | B | C the columns of ``u`` (float32 [tokens, channels]) and
+    S float32 in ``state`` [slots, heads, head_dim, n_state]."""
+    n = u.shape[0]
+    inner = heads * head_dim
+    if (u.shape[1] != inner + 2 * groups * n_state or y.shape != (n, inner)
+            or state.shape[1:] != (heads, head_dim, n_state) or proj.shape[0] != n):
+        raise KernelError("ssm_scan: shapes do not fit")
+    _check(_lib("recurrent").mf_ssm_scan(
+        _f32(u, "u"), _f32(proj, "proj"), proj.shape[1], int(dt_off), u.shape[1],
+        _f32(dt_bias, "dt_bias"), _f32(a_log, "a_log"), _f32(d_skip, "d_skip"), _f32(state, "state"),
+        _i32(cu_seqlens, "cu_seqlens"), _i32(slots, "slots"), _f32(y, "y"), int(n_rows), heads,
+        head_dim, n_state, groups, _stream()), "ssm_scan")
+
+
+def gated_group_norm(y: torch.Tensor, proj: torch.Tensor, z_off: int, weight: torch.Tensor,
+                     out: torch.Tensor, groups: int, eps: float) -> None:
+    """v = y * silu(z), z the columns z_off .. of ``proj``; each of ``groups`` equal parts of v
+    divided by its root mean square, times ``weight``."""
+    n, inner = y.shape
+    if out.shape != (n, inner) or weight.numel() != inner or inner % groups != 0:
+        raise KernelError("gated_group_norm: shapes do not fit")
+    _check(_lib("recurrent").mf_gated_group_norm(
+        _f32(y, "y"), _f32(proj, "proj"), proj.shape[1], int(z_off), _f32(weight, "weight"),
+        _ptr(out, "out"), dtype_code(out.dtype), n, inner, int(groups), float(eps), _stream()),
+        "gated_group_norm")
+
+
+# ---------------------------------------------------------------------------------------
+# between an attention mixer's projection and its attention (csrc/mixer_prep.cu)
+# ---------------------------------------------------------------------------------------
+class _PrepArgs(ctypes.Structure):
+    _fields_ = ([("proj", c_void_p), ("in_width", c_longlong)] +
+                [(n, c_void_p) for n in ("positions", "token_row", "seq_end", "inv_freq", "q_norm_w",
+                                         "k_norm_w", "q_out", "k_out", "v_out", "k_cache", "v_cache",
+                                         "page_table")] +
+                [(n, c_int) for n in ("table_stride", "ring", "q_off", "n_heads", "qw", "q_norm_n",
+                                      "q_rot_off", "k_off", "n_kv", "kw", "k_norm_n", "k_rot_off",
+                                      "v_off", "vw", "v_from_k", "rot_dims", "rot_style")] +
+                [("rot_mag", c_float), ("eps", c_float), ("status", c_void_p)])
+
+
+def qk_prepare(proj: torch.Tensor, positions: torch.Tensor, token_row: torch.Tensor,
+               seq_end: torch.Tensor, q_out: torch.Tensor, k_out: Optional[torch.Tensor],
+               v_out: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
+               v_cache: Optional[torch.Tensor], page_table: Optional[torch.Tensor],
+               table_stride: int, ring: int, *, q_off: int, n_heads: int, q_width: int,
+               k_off: int, n_kv: int, k_width: int, v_off: int, v_width: int, v_from_k: bool,
+               q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor], eps: float,
+               inv_freq: Optional[torch.Tensor], rot_dims: int, rot_style: int, rot_magnitude: float,
+               q_rot_off: int, k_rot_off: int, status: torch.Tensor) -> None:
+    """From the float32 projection rows: the query segment (``n_heads`` heads of ``q_width`` at
+    column ``q_off``) and the key segment (``n_kv`` heads of ``k_width`` at ``k_off``), each with
+    its first ``len(norm weight)`` elements RMS-normed as a whole, ``rot_dims`` dimensions of
+    every head rotated from ``q_rot_off`` / ``k_rot_off`` on; values from column ``v_off`` or,
+    with ``v_from_k``, the first ``v_width`` elements of each prepared key head.  Writes q, the
+    step's k and v, and the cache's pages."""
+    n = proj.shape[0]
+    dt = q_out.dtype
+    for t in (k_out, v_out, k_cache, v_cache):
+        if t is not None and t.dtype != dt:
+            raise KernelError("qk_prepare: q, k, v and the cache must share one dtype")
+    if q_out.numel() != n * n_heads * q_width:
+        raise KernelError("qk_prepare: q has the wrong size")
+    if k_cache is not None and (k_cache.shape[-1] != k_width or v_cache.shape[-1] != v_width
+                                or k_cache.shape[1] != n_kv):
+        raise KernelError("qk_prepare: the cache has other key or value widths")
+    need = max(q_off + n_heads * q_width, k_off + n_kv * k_width,
+               0 if v_from_k else v_off + n_kv * v_width)
+    if proj.dim() != 2 or proj.shape[1] < need:
+        raise KernelError("qk_prepare: the projection is narrower than its segments")
+    a = _PrepArgs()
+    a.proj, a.in_width = _f32(proj, "proj"), proj.shape[1]
+    a.positions, a.token_row = _i32(positions, "positions"), _i32(token_row, "token_row")
+    a.seq_end, a.inv_freq = _i32(seq_end, "seq_end"), _f64(inv_freq, "inv_freq")
+    a.q_norm_w, a.k_norm_w = _f32(q_norm, "q_norm"), _f32(k_norm, "k_norm")
+    a.q_out, a.k_out, a.v_out = _ptr(q_out, "q_out"), _ptr(k_out, "k_out"), _ptr(v_out, "v_out")
+    a.k_cache, a.v_cache = _ptr(k_cache, "k_cache"), _ptr(v_cache, "v_cache")
+    a.page_table, a.table_stride, a.ring = _i32(page_table, "page_table"), int(table_stride), int(ring)
+    a.q_off, a.n_heads, a.qw = int(q_off), int(n_heads), int(q_width)
+    a.q_norm_n = q_norm.numel() if q_norm is not None else 0
+    a.q_rot_off = int(q_rot_off)
+    a.k_off, a.n_kv, a.kw = int(k_off), int(n_kv), int(k_width)
+    a.k_norm_n = k_norm.numel() if k_norm is not None else 0
+    a.k_rot_off = int(k_rot_off)
+    a.v_off, a.vw, a.v_from_k = int(v_off), int(v_width), 1 if v_from_k else 0
+    a.rot_dims, a.rot_style = int(rot_dims), int(rot_style)
+    a.rot_mag, a.eps = float(rot_magnitude), float(eps)
+    a.status = _i32(status, "status")
+    _check(_lib("mixer_prep").mf_qk_prepare(ctypes.addressof(a), n, dtype_code(dt), _stream()),
+           "qk_prepare")
+
+
+class _HeadLinearArgs(ctypes.Structure):
+    _fields_ = ([(n, c_void_p) for n in ("x", "w", "y", "gate")] +
+                [(n, c_longlong) for n in ("x_row", "y_row", "gate_row")] +
+                [(n, c_int) for n in ("x_head", "x_off", "y_head", "gate_off", "n_tokens", "heads",
+                                      "J", "D", "tail", "x_tail_off")])
+
+
+def head_linear(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, *, x_head: int, x_off: int,
+                y_head: int, gate: Optional[torch.Tensor] = None, gate_off: int = 0,
+                tail: int = 0, x_tail_off: int = 0) -> None:
+    """y[t][h][j] = sum_d w[h][j][d] * x[t][h * x_head + x_off + d] for every head (``w``
+    [heads, J, D]; ``x`` and ``y`` 2-D rows, head h of y at column h * y_head), times
+    sigmoid(gate[t][gate_off + h * J + j]) if ``gate`` (float32 rows) is given; then ``tail``
+    elements x[t][h * x_head + x_tail_off ..] copied behind the J outputs."""
+    heads, J, D = w.shape
+    n = x.shape[0]
+    if x.dtype != w.dtype or y.dtype != x.dtype or y.shape[0] != n:
+        raise KernelError("head_linear: x, w and y must share one dtype and row count")
+    if (heads - 1) * x_head + x_off + D > x.shape[1] or (heads - 1) * y_head + J + tail > y.shape[1]:
+        raise KernelError("head_linear: a head reaches beyond its row")
+    a = _HeadLinearArgs()
+    a.x, a.w, a.y, a.gate = _ptr(x, "x"), _ptr(w, "w"), _ptr(y, "y"), _f32(gate, "gate")
+    a.x_row, a.y_row = x.shape[1], y.shape[1]
+    a.gate_row = gate.shape[1] if gate is not None else 0
+    a.x_head, a.x_off, a.y_head, a.gate_off = int(x_head), int(x_off), int(y_head), int(gate_off)
+    a.n_tokens, a.heads, a.J, a.D = n, heads, J, D
+    a.tail, a.x_tail_off = int(tail), int(x_tail_off)
+    _check(_lib("mixer_prep").mf_head_linear(ctypes.addressof(a), dtype_code(x.dtype), _stream()),
+           "head_linear")
+
+
+# ---------------------------------------------------------------------------------------
 # sampling
 # ---------------------------------------------------------------------------------------
 # ---------------------------------------------------------------------------------------
@@ -778,10 +975,12 @@ def sink_attention_packed(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, row
                           row_pos: torch.Tensor, cu_seqlens: torch.Tensor, out: torch.Tensor,
                           r1: Optional[torch.Tensor], r2: Optional[torch.Tensor], n_heads: int,
                           n_kv: int, head_dim: int, value_dim: int, window: int, chunk: int,
-                          sink: bool, scale: float) -> None:
+                          sink: bool, scale: float, sink_logit: Optional[torch.Tensor] = None,
+                          softcap: float = 0.0) -> None:
     """Attention of the step's own packed keys and values (whole prompts): scores
     (q . k) * scale - r1 ln(1 + r2 (i - j)), causal, optional window and chunk mask, a sink
-    of score 0 in the softmax if ``sink``."""
+    of score 0 in the softmax if ``sink`` (of score ``sink_logit[h]`` if given), the scores
+    soft-capped first (cap * tanh(s / cap)) if ``softcap`` > 0."""
     rows = q.shape[0]
     if out.shape != (rows, n_heads * value_dim) or (r1 is None) != (r2 is None):
         raise KernelError("sink_attention_packed: shapes do not fit")
@@ -789,7 +988,8 @@ def sink_attention_packed(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, row
         _ptr(q, "q"), _ptr(k, "k"), _ptr(v, "v"), _i32(row_seq, "row_seq"), _i32(row_pos, "row_pos"),
         _i32(cu_seqlens, "cu_seqlens"), _ptr(out, "out"), _f32(r1, "r1"), _f32(r2, "r2"), rows,
         n_heads, n_kv, head_dim, value_dim, int(window), int(chunk), 1 if sink else 0, float(scale),
-        dtype_code(q.dtype), _stream()), "sink_attention_packed")
+        _f32(sink_logit, "sink_logit"), float(softcap), dtype_code(q.dtype), _stream()),
+        "sink_attention_packed")
 
 
 def sink_attention_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
@@ -797,7 +997,8 @@ def sink_attention_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
                          table_stride: int, ring: int, out: torch.Tensor,
                          r1: Optional[torch.Tensor], r2: Optional[torch.Tensor], n_heads: int,
                          n_kv: int, head_dim: int, value_dim: int, window: int, chunk: int,
-                         sink: bool, scale: float) -> None:
+                         sink: bool, scale: float, sink_logit: Optional[torch.Tensor] = None,
+                         softcap: float = 0.0) -> None:
     """The same over the paged cache: every row of ``q`` is a query at its own position."""
     rows = q.shape[0]
     if out.shape != (rows, n_heads * value_dim) or (r1 is None) != (r2 is None):
@@ -806,8 +1007,8 @@ def sink_attention_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
         _ptr(q, "q"), _ptr(k_cache, "k_cache"), _ptr(v_cache, "v_cache"), _i32(row_seq, "row_seq"),
         _i32(row_pos, "row_pos"), _i32(page_table, "page_table"), int(table_stride), int(ring),
         _ptr(out, "out"), _f32(r1, "r1"), _f32(r2, "r2"), rows, n_heads, n_kv, head_dim, value_dim,
-        int(window), int(chunk), 1 if sink else 0, float(scale), dtype_code(q.dtype), _stream()),
-        "sink_attention_paged")
+        int(window), int(chunk), 1 if sink else 0, float(scale), _f32(sink_logit, "sink_logit"),
+        float(softcap), dtype_code(q.dtype), _stream()), "sink_attention_paged")
 
 
 def sink_attention_mma_supported(dtype: torch.dtype, head_dim: int, value_dim: int) -> bool:

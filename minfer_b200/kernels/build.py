@@ -37,6 +37,8 @@ LIBRARIES = {
     "attention_prefill": ("attention_prefill.cu", []),
     "attention_prefill_tc": ("attention_prefill_tc.cu", []),
     "attention_sink": ("attention_sink.cu", []),
+    "recurrent": ("recurrent.cu", []),
+    "mixer_prep": ("mixer_prep.cu", []),
 }
 
 

@@ -47,6 +47,8 @@ class Model:
         self.after_embedding = (build_part("model", plan.after_embedding)
                                 if plan.after_embedding is not None else None)
         self.on_logits = build_part("model", plan.on_logits) if plan.on_logits is not None else None
+        self.pass_injection = (build_part("model", plan.pass_injection)
+                               if plan.pass_injection is not None else None)
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[Linear] = None
         self.device: Optional[torch.device] = None
@@ -73,7 +75,8 @@ class Model:
 
     def model_parts(self) -> List[Any]:
         """The plan's parts around the blocks that this model has."""
-        return [part for part in (self.after_embedding, self.on_logits) if part is not None]
+        return [part for part in (self.after_embedding, self.on_logits, self.pass_injection)
+                if part is not None]
 
     def ignorable_tensors(self) -> List[str]:
         """Names a checkpoint may hold without being used: a separate head beside tied

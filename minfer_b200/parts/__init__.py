@@ -4,21 +4,31 @@ from .attention import Attention
 from .base import (Block, CacheRequest, CacheView, CallBinding, FeedForward, Mixer, Norm, Part,
                    PositionEncoding, StateRequest, StepContext)
 from .block import PreNormBlock
+from .latent_attention import LatentAttention
 from .linear import Linear
+from .mamba2 import Mamba2
 from .mlp import DenseMlp, GatedMlp
 from .norm import RmsNorm
 from .positions import LearnedPositions
+from .qknorm_attention import QkNormAttention
 from .rotary import NoPosition, Rotary
 from .shift import TokenShift
 from .sink_attention import SinkAttention
+from .stream import EmbeddingNorm, LogitSoftcap, PassInjection
 
 register_part("norm", "rms_norm", RmsNorm, replace=True)
 register_part("position", "rotary", Rotary, replace=True)
 register_part("position", "none", NoPosition, replace=True)
 register_part("mixer", "attention", Attention, replace=True)
 register_part("mixer", "sink_attention", SinkAttention, replace=True)
+register_part("mixer", "qk_norm_attention", QkNormAttention, replace=True)
+register_part("mixer", "latent_attention", LatentAttention, replace=True)
+register_part("mixer", "mamba2", Mamba2, replace=True)
 register_part("feed_forward", "gated_mlp", GatedMlp, replace=True)
 register_part("feed_forward", "dense_mlp", DenseMlp, replace=True)
 register_part("model", "learned_positions", LearnedPositions, replace=True)
+register_part("model", "embedding_norm", EmbeddingNorm, replace=True)
+register_part("model", "logit_softcap", LogitSoftcap, replace=True)
+register_part("model", "pass_injection", PassInjection, replace=True)
 register_part("block", "pre_norm", lambda layer, **options: PreNormBlock(layer, **options),
               replace=True)

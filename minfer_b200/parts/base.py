@@ -173,6 +173,12 @@ class ModelPart(Part):
     def forward_inplace(self, x: torch.Tensor, ctx: "StepContext") -> None:
         raise NotImplementedError
 
+    def forward(self, x: torch.Tensor, ctx: "StepContext") -> torch.Tensor:
+        """The tensor that goes on.  By default ``x`` itself, changed in place; a part whose
+        kernel wants an output of its own returns that instead."""
+        self.forward_inplace(x, ctx)
+        return x
+
     def embedding_rows(self, ctx: "StepContext"):
         """For a part that runs after the embedding and only adds a table's rows to the residual
         stream: (table [m, width], index int32 [tokens]), which the embedding kernel then adds

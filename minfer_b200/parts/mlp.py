@@ -1,4 +1,5 @@
-"""Gated feed-forward: down( act(gate(x)) * up(x) ), no biases.
+"""Gated feed-forward: down( act(gate(x)) * up(x) ), no biases; act is silu or the tanh form of
+gelu.
 
 The reference builds it as silu + mul that its fusion pass folds into SwiGLU
 (src/models/qwen2/graph.rs:154-175, src/graph/fusion.rs:37-87), with
@@ -25,31 +26,36 @@ class GatedMlp(FeedForward):
     def libraries(self, dtype: torch.dtype) -> List[str]:
         return ["ops", "gemm_tc"] if dtype == torch.bfloat16 else ["ops", "gemm_simt"]
 
+    ACTIVATIONS = ("silu", "gelu_tanh")
+
     def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu",
-                 init_std: float = 0.02):
-        if activation != "silu":
-            raise ValueError(f"the gated feed-forward has the 'silu' activation only, got "
+                 init_std: float = 0.02, gate_name: str = "mlp.gate_proj.weight",
+                 up_name: str = "mlp.up_proj.weight", down_name: str = "mlp.down_proj.weight"):
+        """``activation`` of the gate: "silu", or "gelu_tanh" = 0.5 z (1 + tanh(sqrt(2/pi) (z +
+        0.044715 z^3))).  The tensors' names (behind the layer's prefix) are parameters."""
+        if activation not in self.ACTIVATIONS:
+            raise ValueError(f"the gated feed-forward has the activations {self.ACTIVATIONS}, got "
                              f"{activation!r}")
         self.hidden_size = int(hidden_size)
         self.intermediate_size = int(intermediate_size)
+        self.activation = activation
+        self.gate_name, self.up_name, self.down_name = gate_name, up_name, down_name
         self.init_std = float(init_std)
         self.interleaved = False
         self.gate_up: Optional[Linear] = None
         self.down: Optional[Linear] = None
 
     def tensor_specs(self, prefix: str) -> List[TensorSpec]:
-        p = f"{prefix}mlp."
         init = Init(0.0, self.init_std)
-        return [TensorSpec(f"{p}gate_proj.weight", (self.intermediate_size, self.hidden_size),
+        return [TensorSpec(f"{prefix}{self.gate_name}", (self.intermediate_size, self.hidden_size),
                            MATRIX, init),
-                TensorSpec(f"{p}up_proj.weight", (self.intermediate_size, self.hidden_size),
+                TensorSpec(f"{prefix}{self.up_name}", (self.intermediate_size, self.hidden_size),
                            MATRIX, init),
-                TensorSpec(f"{p}down_proj.weight", (self.hidden_size, self.intermediate_size),
+                TensorSpec(f"{prefix}{self.down_name}", (self.hidden_size, self.intermediate_size),
                            MATRIX, init)]
 
     def load(self, prefix: str, weights: Dict[str, torch.Tensor]) -> None:
-        p = f"{prefix}mlp."
-        g, u = weights[f"{p}gate_proj.weight"], weights[f"{p}up_proj.weight"]
+        g, u = weights[f"{prefix}{self.gate_name}"], weights[f"{prefix}{self.up_name}"]
         if g.dtype != u.dtype:
             g, u = g.to(torch.float32), u.to(torch.float32)
         # bfloat16: rows alternate gate, up so that the tensor-core kernel's epilogue finds a
@@ -60,19 +66,18 @@ class GatedMlp(FeedForward):
         else:
             packed = torch.cat([g, u], dim=0)
         self.gate_up = Linear(packed.contiguous())
-        self.down = Linear(weights[f"{p}down_proj.weight"])
+        self.down = Linear(weights[f"{prefix}{self.down_name}"])
         self.accepts_row_scale = self.interleaved and self.gate_up.takes_row_scale()
 
     def export(self, prefix: str) -> Dict[str, torch.Tensor]:
-        p = f"{prefix}mlp."
         w = self.gate_up.weight
         if self.interleaved:
             pairs = w.view(self.intermediate_size, 2, self.hidden_size)
             gate, up = pairs[:, 0], pairs[:, 1]
         else:
             gate, up = w[:self.intermediate_size], w[self.intermediate_size:]
-        return {f"{p}gate_proj.weight": gate, f"{p}up_proj.weight": up,
-                f"{p}down_proj.weight": self.down.weight}
+        return {f"{prefix}{self.gate_name}": gate, f"{prefix}{self.up_name}": up,
+                f"{prefix}{self.down_name}": self.down.weight}
 
     def forward_add(self, x: torch.Tensor, ctx: StepContext, residual: torch.Tensor) -> None:
         from ..kernels import gemm
@@ -82,15 +87,16 @@ class GatedMlp(FeedForward):
         rs = ctx.input_scale                       # the norm's 1/rms, if this product is to apply it
         if (self.interleaved and x.shape[0] > 0 and gemm.use_tensor_cores()
                 and K.gemm_tc_supported(x, w)):
+            epi = K.gated_epilogue(self.activation)
             if rs is not None:
-                K.gemm_tc_fused(x, w, None, act, K.EPI_SWIGLU, gemm.status_word(x.device), row_scale=rs)
+                K.gemm_tc_fused(x, w, None, act, epi, gemm.status_word(x.device), row_scale=rs)
             else:
-                K.gemm_tc(x, w, None, act, K.EPI_SWIGLU, gemm.status_word(x.device))
+                K.gemm_tc(x, w, None, act, epi, gemm.status_word(x.device))
         else:
             if rs is not None:
                 raise K.KernelError("a row scale needs the tensor-core product")
             gu = self.gate_up.forward(x, ctx.act_dtype)
-            K.swiglu(gu, act, self.interleaved)
+            K.swiglu(gu, act, self.interleaved, self.activation)
         target = ctx.extras.pop("prepare_for", None)
         if target is not None:
             settle_pending(ctx, residual)

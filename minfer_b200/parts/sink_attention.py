@@ -19,6 +19,7 @@ ring of that many positions plus what a step may add, as for a windowed layer.
 from __future__ import annotations
 
 import os
+from dataclasses import dataclass
 from typing import Dict, List, Optional
 
 import torch
@@ -41,6 +42,117 @@ PAGED_PROMPT_MIN_TOKENS = int(os.environ.get("MINFER_B200_SINK_PAGED_PROMPT_MIN_
 PAGED_TCGEN05_MIN_TOKENS = int(os.environ.get("MINFER_B200_SINK_PAGED_TCGEN05_MIN_TOKENS", "160"))
 # "tcgen05" (tensor memory, where the sizes allow) or "mma" (the mma.sync kernel) for prompts
 PROMPT_KERNEL = os.environ.get("MINFER_B200_SINK_PROMPT_KERNEL", "tcgen05")
+
+
+@dataclass
+class ScoreSpec:
+    """Sizes and score modifiers of one attention: what ``scored_attention`` runs.  ``sink``: a
+    key without a value in the softmax, of score 0 or of ``sink_logit[h]`` (float32 per head);
+    ``softcap`` > 0: scores pass through cap * tanh(s / cap) before the bias; ``r1``, ``r2``: the
+    logarithmic distance bias per head."""
+
+    n_heads: int
+    n_kv_heads: int
+    head_dim: int
+    value_dim: int
+    scale: float
+    window: int = 0
+    chunk: int = 0
+    sink: bool = False
+    r1: Optional[torch.Tensor] = None
+    r2: Optional[torch.Tensor] = None
+    sink_logit: Optional[torch.Tensor] = None
+    softcap: float = 0.0
+
+    def reach(self) -> int:
+        """Positions a query may look back, itself included (0: no bound)."""
+        bounds = [b for b in (self.chunk, self.window) if b > 0]
+        return min(bounds) if bounds else 0
+
+
+def scored_attention(spec: ScoreSpec, q: torch.Tensor, k_step: Optional[torch.Tensor],
+                     v_step: Optional[torch.Tensor], cache, ctx: StepContext, o: torch.Tensor) -> None:
+    """o = attention of the step's queries ``q`` [tokens, heads, head_dim] (already normed,
+    rotated, whatever the mixer does to them): over the step's own packed keys and values for
+    whole prompts (``ctx.from_start``), over the cache's pages otherwise (it holds the step's
+    keys by then; every token is a query at its own position).  Picks the kernel by precision,
+    sizes and the shape of the step; every choice computes the same function."""
+    nh, nk, hd, vd = spec.n_heads, spec.n_kv_heads, spec.head_dim, spec.value_dim
+    act = q.dtype
+    own_kv = ctx.from_start
+    r1, r2 = spec.r1, spec.r2
+    # the tensor-core kernels take neither a soft cap nor a learned score of the sink
+    plain_scores = spec.softcap == 0.0 and spec.sink_logit is None
+    tensor_cores = (plain_scores and K.sink_attention_mma_supported(act, hd, vd)
+                    and not FORCE_GENERIC)
+    # prompts: the tcgen05 kernel where keys and values have one size it takes, else mma.sync
+    tcgen05 = (tensor_cores and PROMPT_KERNEL != "mma"
+               and K.sink_attention_tc_supported(act, hd, vd))
+    if own_kv and tcgen05:
+        K.sink_attention_tc(q, k_step, v_step, ctx.cu_seqlens, None, None, 0, 0, o, r1, r2,
+                            ctx.n_rows, ctx.max_row_tokens, nh, nk, hd, spec.window, spec.chunk,
+                            spec.sink, spec.scale, ctx.status)
+        return
+    if own_kv and tensor_cores:
+        K.sink_attention_mma(q, k_step, v_step, ctx.cu_seqlens, None, None, 0, 0, o, r1, r2,
+                             ctx.n_rows, ctx.max_row_tokens, nh, nk, hd, vd, spec.window,
+                             spec.chunk, spec.sink, spec.scale)
+        return
+    if own_kv:
+        K.sink_attention_packed(q, k_step, v_step, ctx.token_row, ctx.positions, ctx.cu_seqlens, o,
+                                r1, r2, nh, nk, hd, vd, spec.window, spec.chunk, spec.sink,
+                                spec.scale, sink_logit=spec.sink_logit, softcap=spec.softcap)
+        return
+    reach = spec.reach()
+    if cache.ring and ctx.max_row_tokens > cache.ring - reach + 1:
+        raise K.KernelError(
+            f"a sequence brings {ctx.max_row_tokens} tokens, but a ring of {cache.ring} "
+            f"positions with a reach of {reach} takes {cache.ring - reach + 1} a step "
+            f"(the engine runs longer rows in portions)")
+    if tcgen05 and not ctx.single_token and ctx.n_tokens >= PAGED_TCGEN05_MIN_TOKENS:
+        K.sink_attention_tc(q, cache.k, cache.v, ctx.cu_seqlens, ctx.seq_end, cache.page_table,
+                            cache.table_stride, cache.ring, o, r1, r2, ctx.n_rows,
+                            ctx.max_row_tokens, nh, nk, hd, spec.window, spec.chunk, spec.sink,
+                            spec.scale, ctx.status)
+        return
+    if tensor_cores and not ctx.single_token and ctx.n_tokens >= PAGED_PROMPT_MIN_TOKENS:
+        # rows of several tokens: query tiles of the step's rows over the cache's pages
+        K.sink_attention_mma(q, cache.k, cache.v, ctx.cu_seqlens, ctx.seq_end, cache.page_table,
+                             cache.table_stride, cache.ring, o, r1, r2, ctx.n_rows,
+                             ctx.max_row_tokens, nh, nk, hd, vd, spec.window, spec.chunk,
+                             spec.sink, spec.scale)
+        return
+    if tensor_cores and nh // nk <= 16:
+        # single queries: the heads of a key/value head are the rows of the product
+        K.sink_attention_decode(q, cache.k, cache.v, ctx.token_row, ctx.positions,
+                                cache.page_table, cache.table_stride, cache.ring, o, r1, r2, nh,
+                                nk, hd, vd, spec.window, spec.chunk, spec.sink, spec.scale,
+                                reach if reach > 0 else ctx.max_end)
+        return
+    K.sink_attention_paged(q, cache.k, cache.v, ctx.token_row, ctx.positions, cache.page_table,
+                           cache.table_stride, cache.ring, o, r1, r2, nh, nk, hd, vd, spec.window,
+                           spec.chunk, spec.sink, spec.scale, sink_logit=spec.sink_logit,
+                           softcap=spec.softcap)
+
+
+def project_out(out: Linear, o: torch.Tensor, ctx: StepContext, residual: torch.Tensor) -> None:
+    """residual += out(o), in whichever of three ways fits the step: completed here with the next
+    norm's input prepared (``ctx.extras["prepare_for"]``), left as K splits for the next kernel to
+    add (``Pending``), or added by the product's epilogue."""
+    target = ctx.extras.pop("prepare_for", None)
+    if target is not None:
+        # the product completes the residual and prepares the next norm's input
+        settle_pending(ctx, residual)
+        prepared = out.accumulate_prepared(o, residual, target)
+        if prepared is not None:
+            ctx.extras["prepared"] = prepared
+            return
+    pending = out.partial_sums(o)
+    if pending is None:
+        out.forward(o, torch.float32, out=residual, accumulate=True)
+    else:
+        settle_pending(ctx, residual)          # never two at once
+        ctx.extras["pending"] = pending
 
 
 class SinkAttention(Mixer):
@@ -89,8 +201,7 @@ class SinkAttention(Mixer):
     # ---- how far back a query may look ----------------------------------------------------
     def reach(self) -> int:
         """Positions a query may look back, itself included (0: no bound)."""
-        bounds = [b for b in (self.chunk, self.window) if b > 0]
-        return min(bounds) if bounds else 0
+        return self.scores().reach()
 
     # ---- weights ----------------------------------------------------------------------
     def tensor_specs(self, prefix: str) -> List[TensorSpec]:
@@ -169,70 +280,13 @@ class SinkAttention(Mixer):
                             nh, nk, hd, vd, self.norm_eps, self.qk_norm, ctx.status,
                             n_partials=n_partials)
         o = torch.empty((n, nh * vd), dtype=act, device=dev)
-        tensor_cores = (K.sink_attention_mma_supported(act, hd, vd) and not FORCE_GENERIC)
-        # prompts: the tcgen05 kernel where keys and values have one size it takes, else mma.sync
-        tcgen05 = (tensor_cores and PROMPT_KERNEL != "mma"
-                   and K.sink_attention_tc_supported(act, hd, vd))
-        if own_kv and tcgen05:
-            K.sink_attention_tc(q, k_step, v_step, ctx.cu_seqlens, None, None, 0, 0, o, self.r1,
-                                self.r2, ctx.n_rows, ctx.max_row_tokens, nh, nk, hd, self.window,
-                                self.chunk, self.sink, self.scale, ctx.status)
-        elif own_kv and tensor_cores:
-            K.sink_attention_mma(q, k_step, v_step, ctx.cu_seqlens, None, None, 0, 0, o, self.r1,
-                                 self.r2, ctx.n_rows, ctx.max_row_tokens, nh, nk, hd, vd,
-                                 self.window, self.chunk, self.sink, self.scale)
-        elif own_kv:
-            K.sink_attention_packed(q, k_step, v_step, ctx.token_row, ctx.positions,
-                                    ctx.cu_seqlens, o, self.r1, self.r2, nh, nk, hd, vd,
-                                    self.window, self.chunk, self.sink, self.scale)
-        else:
-            reach = self.reach()
-            if cache.ring and ctx.max_row_tokens > cache.ring - reach + 1:
-                raise K.KernelError(
-                    f"a sequence brings {ctx.max_row_tokens} tokens, but a ring of {cache.ring} "
-                    f"positions with a reach of {reach} takes {cache.ring - reach + 1} a step "
-                    f"(the engine runs longer rows in portions)")
-            if tcgen05 and not ctx.single_token and ctx.n_tokens >= PAGED_TCGEN05_MIN_TOKENS:
-                K.sink_attention_tc(q, cache.k, cache.v, ctx.cu_seqlens, ctx.seq_end,
-                                    cache.page_table, cache.table_stride, cache.ring, o, self.r1,
-                                    self.r2, ctx.n_rows, ctx.max_row_tokens, nh, nk, hd,
-                                    self.window, self.chunk, self.sink, self.scale, ctx.status)
-                self._project_out(o, ctx, residual)
-                return
-            if tensor_cores and not ctx.single_token and ctx.n_tokens >= PAGED_PROMPT_MIN_TOKENS:
-                # rows of several tokens: query tiles of the step's rows over the cache's pages
-                K.sink_attention_mma(q, cache.k, cache.v, ctx.cu_seqlens, ctx.seq_end,
-                                     cache.page_table, cache.table_stride, cache.ring, o, self.r1,
-                                     self.r2, ctx.n_rows, ctx.max_row_tokens, nh, nk, hd, vd,
-                                     self.window, self.chunk, self.sink, self.scale)
-                self._project_out(o, ctx, residual)
-                return
-            if tensor_cores and nh // nk <= 16:
-                # single queries: the heads of a key/value head are the rows of the product
-                K.sink_attention_decode(q, cache.k, cache.v, ctx.token_row, ctx.positions,
-                                        cache.page_table, cache.table_stride, cache.ring, o,
-                                        self.r1, self.r2, nh, nk, hd, vd, self.window, self.chunk,
-                                        self.sink, self.scale, reach if reach > 0 else ctx.max_end)
-                self._project_out(o, ctx, residual)
-                return
-            K.sink_attention_paged(q, cache.k, cache.v, ctx.token_row, ctx.positions,
-                                   cache.page_table, cache.table_stride, cache.ring, o, self.r1,
-                                   self.r2, nh, nk, hd, vd, self.window, self.chunk, self.sink,
-                                   self.scale)
+        scored_attention(self.scores(), q, k_step, v_step, cache, ctx, o)
         self._project_out(o, ctx, residual)
 
+    def scores(self) -> "ScoreSpec":
+        return ScoreSpec(n_heads=self.n_heads, n_kv_heads=self.n_kv_heads, head_dim=self.head_dim,
+                         value_dim=self.value_dim, scale=self.scale, window=self.window,
+                         chunk=self.chunk, sink=self.sink, r1=self.r1, r2=self.r2)
+
     def _project_out(self, o: torch.Tensor, ctx: StepContext, residual: torch.Tensor) -> None:
-        target = ctx.extras.pop("prepare_for", None)
-        if target is not None:
-            # the product completes the residual and prepares the next norm's input
-            settle_pending(ctx, residual)
-            prepared = self.out.accumulate_prepared(o, residual, target)
-            if prepared is not None:
-                ctx.extras["prepared"] = prepared
-                return
-        pending = self.out.partial_sums(o)
-        if pending is None:
-            self.out.forward(o, torch.float32, out=residual, accumulate=True)
-        else:
-            settle_pending(ctx, residual)          # never two at once
-            ctx.extras["pending"] = pending
+        project_out(self.out, o, ctx, residual)

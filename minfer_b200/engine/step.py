@@ -412,13 +412,17 @@ class Engine:
         if cap < max_end:
             cap = ((max_end + 511) // 512) * 512
         key = (n_rows, cap)
+        widths = [(g.ring // PAGE) if g.ring else cap // PAGE for g in self.cache.groups]
+        # a sequence may hold pages beyond this step's bound (a longer step reserved them and now
+        # runs token by token): the graph's page tables are too narrow for it
+        if any(g.max_pages_of(slots) > width for g, width in zip(self.cache.groups, widths)):
+            return None
         entry = self._graphs.get(key)
         if entry is None and key not in self._seen_shapes:
             # the first step of a shape runs kernel by kernel (it also builds libraries and sets
             # kernel attributes, which capture does not allow); the second one is captured
             self._seen_shapes.add(key)
             return None
-        widths = [(g.ring // PAGE) if g.ring else cap // PAGE for g in self.cache.groups]
         counts = [1] * n_rows
         want = [[0]] * n_rows
         fields = self._host_fields(slots, tokens, counts, starts, want, widths)

@@ -232,3 +232,51 @@ def forward(config: Mapping, weights: Mapping[str, torch.Tensor], tokens: List[i
     if cap:
         logits = float(cap) * torch.tanh(logits / float(cap))
     return logits
+
+
+# ---- attention over given queries and keys (for tests of the attention kernels alone) ----------
+def scored_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_pos: List[int],
+                     scale: float, window: int = 0, softcap: float = 0.0,
+                     sink: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """q [nq, H, D], k [nk, G, D], v [nk, G, Dv]; key j is at position j; query a at position
+    q_pos[a] sees j <= q_pos[a] (and q_pos[a] - j < window if window > 0).  ``sink`` [H]: a score
+    in the softmax's denominator without a value.  One (query, head) at a time."""
+    nq, H, _ = q.shape
+    G = k.shape[1]
+    out = torch.zeros((nq, H, v.shape[-1]), dtype=q.dtype)
+    for a in range(nq):
+        i = q_pos[a]
+        lo = max(0, i - window + 1) if window > 0 else 0
+        for h in range(H):
+            g = h // (H // G)
+            s = (k[lo:i + 1, g] @ q[a, h]) * scale
+            if softcap > 0:
+                s = softcap * torch.tanh(s / softcap)
+            top = s.max() if sink is None else torch.maximum(s.max(), sink[h])
+            e = torch.exp(s - top)
+            den = e.sum() if sink is None else e.sum() + torch.exp(sink[h] - top)
+            out[a, h] = (e @ v[lo:i + 1, g]) / den
+    return out
+
+
+def load_folder(folder: str, dtype: torch.dtype = torch.float64):
+    import json
+    import os
+    from safetensors import safe_open
+    with open(os.path.join(folder, "config.json")) as f:
+        cfg = json.load(f)
+    weights = {}
+    with safe_open(os.path.join(folder, "model.safetensors"), framework="pt") as f:
+        for name in f.keys():
+            weights[name] = f.get_tensor(name).to(dtype)
+    return cfg, weights
+
+
+def generate_greedy(config: Mapping, w: Mapping[str, torch.Tensor], prompt: List[int],
+                    n_new: int) -> List[int]:
+    ids, out = list(prompt), []
+    for _ in range(n_new):
+        tok = int(torch.argmax(forward(config, w, ids)[-1]))
+        out.append(tok)
+        ids.append(tok)
+    return out

@@ -1,0 +1,206 @@
+"""Budanex through the engine against the plain implementation, in float32 and bfloat16: whole
+prompts; the last tokens one by one; prompts in portions down to two tokens; batches of unequal
+requests against each alone, one batch after another so that slots, pages and state are used
+again; a mixed step; decoding far past a window's ring; greedy generation through the generator."""
+import pytest
+import torch
+
+import plain_budanex as P
+from budanex_cases import CASES, make_folder
+from helpers import logits_err, random_ids
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = [37, 5, 131, 64, 1, 65, 11]
+
+
+@pytest.fixture(scope="module", params=["A", "B", "C"])
+def case(request):
+    folder = make_folder(request.param)
+    cfg, w = P.load_folder(folder)
+    prompts = [random_ids(n, cfg["vocab"], 500 + i) for i, n in enumerate(LENGTHS)]
+    plain = [P.forward(cfg, w, ids) for ids in prompts]
+    return {"name": request.param, "folder": folder, "cfg": cfg, "w": w, "prompts": prompts,
+            "plain": plain}
+
+
+def _engine(folder, dtype, max_tokens=4096, **kw):
+    from minfer_b200.engine.step import Engine
+    from minfer_b200.model import Model
+    return Engine(Model.from_folder(folder, dtype, "cuda:0"), max_tokens=max_tokens, **kw)
+
+
+def _close(got, want, dtype):
+    err, bound = logits_err(got, want, dtype)
+    assert err < bound, (err, bound)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_whole_prompts_and_every_layer(case, dtype):
+    eng = _engine(case["folder"], dtype)
+    for ids, want in zip(case["prompts"], case["plain"]):
+        s = eng.acquire()
+        got = eng.step([s], [ids], [list(range(len(ids)))])
+        eng.release(s)
+        assert got.shape == want.shape
+        _close(got, want, dtype)
+    # the residual stream after every run of a layer (a looped layer counts each time)
+    ids = case["prompts"][0]
+    taps, seen = [], []
+    P.forward(case["cfg"], case["w"], ids, taps)
+    eng.layer_tap = lambda i, h: seen.append(h.detach().cpu().to(torch.float64))
+    s = eng.acquire()
+    eng.step([s], [ids], [list(range(len(ids)))])
+    eng.release(s)
+    eng.layer_tap = None
+    assert len(seen) == len(taps)
+    for got, want in zip(seen, taps):
+        tol = 3e-5 if dtype == "float32" else 4e-2
+        assert float((got - want).abs().max()) < tol * float(want.abs().max())
+    eng.check_status()
+    eng.cache.check_canaries()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_last_tokens_one_by_one(case, dtype):
+    eng = _engine(case["folder"], dtype)
+    for ids, want in zip(case["prompts"], case["plain"]):
+        n = len(ids)
+        head = max(1, n - 40)
+        s = eng.acquire()
+        rows = [eng.step([s], [ids[:head]], [list(range(head))])]
+        for t in range(head, n):
+            rows.append(eng.step([s], [[ids[t]]], [[0]]))
+        eng.release(s)
+        _close(torch.cat(rows), want, dtype)
+    eng.check_status()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_token_by_token_from_the_first(case, dtype):
+    """Every token a step of its own, from position 0: the first tokens see the zeros before the
+    sequence in the convolution and nothing but themselves (and the sink) in attention."""
+    eng = _engine(case["folder"], dtype)
+    ids, want = case["prompts"][0], case["plain"][0]
+    s = eng.acquire()
+    rows = [eng.step([s], [[t]], [[0]]) for t in ids]
+    eng.release(s)
+    _close(torch.cat(rows), want, dtype)
+    eng.check_status()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("portion", [2, 3, 7, 63, 64, 65])
+def test_prompts_in_portions(case, dtype, portion):
+    eng = _engine(case["folder"], dtype)
+    for ids, want in zip(case["prompts"][:4], case["plain"][:4]):
+        s = eng.acquire()
+        rows = []
+        for lo in range(0, len(ids), portion):
+            part = ids[lo:lo + portion]
+            rows.append(eng.step([s], [part], [list(range(len(part)))]))
+        eng.release(s)
+        _close(torch.cat(rows), want, dtype)
+    eng.check_status()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_unequal_batches_slots_reused(case, dtype):
+    """The prompts' first parts in one step, then one token each; a request that runs out of
+    tokens leaves the batch; the next batch starts in the slots, pages and state the first one
+    gave back.  Every request's logits equal those it has alone."""
+    eng = _engine(case["folder"], dtype, max_tokens=1024, max_seqs=4)
+    prompts, plain = case["prompts"], case["plain"]
+    for batch in ([0, 1, 2], [3, 4, 5, 6], [2, 0], [6, 2, 4]):
+        slots = {r: eng.acquire() for r in batch}
+        heads = {r: max(1, len(prompts[r]) - 9) for r in batch}
+        got = {r: [] for r in batch}
+        out = eng.step([slots[r] for r in batch], [prompts[r][:heads[r]] for r in batch],
+                       [list(range(heads[r])) for r in batch])
+        at = 0
+        for r in batch:
+            got[r].append(out[at:at + heads[r]])
+            at += heads[r]
+        pos = dict(heads)
+        live = [r for r in batch if pos[r] < len(prompts[r])]
+        while live:
+            out = eng.step([slots[r] for r in live], [[prompts[r][pos[r]]] for r in live],
+                           [[0]] * len(live))
+            for i, r in enumerate(live):
+                got[r].append(out[i:i + 1])
+                pos[r] += 1
+            live = [r for r in live if pos[r] < len(prompts[r])]
+        for r in batch:
+            _close(torch.cat(got[r]), plain[r], dtype)
+            eng.release(slots[r])
+    eng.check_status()
+    eng.cache.check_canaries()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_mixed_step_a_new_portion_beside_single_tokens(case, dtype):
+    """One request goes on by 20 tokens while two others go on by one, in the same step."""
+    eng = _engine(case["folder"], dtype)
+    prompts, plain = case["prompts"], case["plain"]
+    a, b, c = 2, 0, 6
+    sa, sb, sc = eng.acquire(), eng.acquire(), eng.acquire()
+    eng.step([sa, sb, sc], [prompts[a][:100], prompts[b][:30], prompts[c][:10]], [[], [], []])
+    out = eng.step([sb, sa, sc], [[prompts[b][30]], prompts[a][100:120], [prompts[c][10]]],
+                   [[0], list(range(20)), [0]])
+    _close(out[0:1], plain[b][30:31], dtype)
+    _close(out[1:21], plain[a][100:120], dtype)
+    _close(out[21:22], plain[c][10:11], dtype)
+    eng.check_status()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_long_decoding_past_the_rings(name, dtype):
+    """330 tokens: a prompt of 70, then one by one far past the windows' rings (and with the
+    state-space layers' state carried all the way); the same in portions of 50 with a ring that
+    has slack for one new position only."""
+    folder = make_folder(name)
+    cfg, w = P.load_folder(folder)
+    ids = random_ids(330, cfg["vocab"], 91)
+    want = P.forward(cfg, w, ids)
+    eng = _engine(folder, dtype, max_tokens=1024)
+    assert any(g.ring and g.ring < 330 for g in eng.cache.groups)
+    s = eng.acquire()
+    rows = [eng.step([s], [ids[:70]], [list(range(70))])]
+    for t in range(70, 330):
+        rows.append(eng.step([s], [[ids[t]]], [[0]]))
+    eng.release(s)
+    _close(torch.cat(rows), want, dtype)
+    eng2 = _engine(folder, dtype, max_tokens=1024, ring_step_tokens=1)
+    s = eng2.acquire()
+    rows = []
+    for lo in range(0, 330, 50):
+        part = ids[lo:lo + 50]
+        rows.append(eng2.step([s], [part], [list(range(len(part)))]))
+    _close(torch.cat(rows), want, dtype)
+    eng.check_status()
+    eng2.check_status()
+    eng2.cache.check_canaries()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_through_the_generator(case, dtype):
+    from helpers import TOL
+    from minfer_b200.engine.generate import Generator
+    from minfer_b200.model import Model
+    from minfer_b200.sampling.params import SamplingParams
+    cfg, w = case["cfg"], case["w"]
+    prompts = [case["prompts"][0], case["prompts"][1], case["prompts"][6]]
+    gen = Generator(Model.from_folder(case["folder"], dtype, "cuda:0"), max_tokens=2048, max_batch=4)
+    got = gen.generate(prompts, 8, SamplingParams.greedy(), stop_token_ids=[])
+    for prompt, res in zip(prompts, got):
+        assert len(res.tokens) == 8
+        ids = list(prompt)
+        for tok in res.tokens:             # each token on the prefix the engine itself produced
+            logits = P.forward(cfg, w, ids)[-1]
+            if dtype == "float32":
+                assert tok == int(torch.argmax(logits))
+            else:
+                slack = 2 * TOL["bfloat16"] * float(logits.abs().max())
+                assert float(logits[tok]) >= float(logits.max()) - slack
+            ids.append(tok)

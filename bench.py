@@ -153,6 +153,13 @@ def decode_bytes(model, batch, context_tokens):
             # at most that many positions back
             seen = min(context_tokens, req.window) if req.window else context_tokens
             kv += req.n_kv_heads * (req.head_dim + (req.value_dim or req.head_dim)) * esz * seen
+        # fixed-size state per sequence (a recurrent mixer's): read and written once a step
+        block = model.blocks[call.layer]
+        for st in (block.state_request() if hasattr(block, "state_request") else ()):
+            n = 1
+            for d in st.shape:
+                n *= d
+            kv += 2 * n * 4
     return weights + batch * kv
 
 
@@ -506,6 +513,228 @@ def workload_furitar(args) -> int:
     return 0
 
 
+# ------------------------------------------------------------------------------------------
+# --workload budanex: the Budanex design beside the Qwen2 decoder at equal width and layer runs
+# ------------------------------------------------------------------------------------------
+# (name, width, attention heads, kv heads, head size, feed-forward width, state-space heads,
+#  latent heads, window): six layers [state-space, latent attention + ff, attention + ff] x 2,
+# the last three run twice (nine layer runs); Qwen2 beside it with nine layers
+BUDANEX_SIZES = [("w2048", 2048, 16, 4, 128, 5632, 64, 16, 1024),
+                 ("w4096", 4096, 32, 8, 128, 11264, 128, 32, 2048)]
+BUDANEX_RUNS = 9
+
+
+def budanex_config(width, heads, kv, dim, ff, ssm_heads, lat_heads, window, vocab):
+    mamba = {"type": "mamba2", "mlp": None,
+             "mixer": {"heads": ssm_heads, "vdim": 64, "state": 128, "groups": 1, "conv": 4,
+                       "norm_groups": 1}}
+    latent = {"type": "latent_attention", "mlp": {"kind": "dense", "ff": ff},
+              "mixer": {"heads": lat_heads, "dim": 64, "rot_dim": 32, "vdim": 64, "kv_rank": 96,
+                        "scale": 96 ** -0.5, "mask": {"size": window},
+                        "rot": {"base": 500000.0, "dims": 32,
+                                "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    attention = {"type": "attention", "mlp": {"kind": "dense", "ff": ff},
+                 "mixer": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim,
+                           "scale": dim ** -0.5, "softcap": 50.0,
+                           "rot": {"base": 1000000.0, "dims": dim // 2}}}
+    return {"architecture": "Budanex", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "logit_softcap": 30.0, "loop": {"start": 3, "stop": 6, "times": 2},
+            "layers": [mamba, latent, attention, mamba, latent, attention]}
+
+
+def budanex_prefill_flops(cfg, tokens):
+    """Matrix-product flops of one whole prompt (head on the last row only), the attention of the
+    visible keys (latent attention in the form it is computed in: one shared key of kv_rank +
+    rot_dim, values of kv_rank, and the two per-head products), and the recurrence."""
+    w, n = cfg["width"], tokens
+    lo, hi, times = cfg["loop"]["start"], cfg["loop"]["stop"], cfg["loop"]["times"]
+    flops = 0.0
+    for i, layer in enumerate(cfg["layers"]):
+        runs = times if lo <= i < hi else 1
+        m = layer["mixer"]
+        if layer["type"] == "mamba2":
+            inner = m["heads"] * m["vdim"]
+            per_token = 2 * w * (2 * inner + 2 * m["groups"] * m["state"] + m["heads"]) + 2 * w * inner
+            per_token += 6 * inner * m["state"]
+            pairs = 0.0
+        elif layer["type"] == "attention":
+            per_token = 2 * w * ((m["heads"] + m["kv_heads"]) * m["dim"] + m["kv_heads"] * m["vdim"])
+            per_token += 2 * w * m["heads"] * m["vdim"]
+            pairs = m["heads"] * 2 * (m["dim"] + m["vdim"]) * n * (n + 1) / 2
+        else:
+            h, rank, rd = m["heads"], m["kv_rank"], m["rot_dim"]
+            per_token = 2 * w * (h * (m["dim"] + rd) + rank + rd + h * m["vdim"]) + 2 * w * h * m["vdim"]
+            per_token += 2 * h * rank * (m["dim"] + m["vdim"])
+            c = m["mask"]["size"]
+            seen = n * (n + 1) / 2 if n <= c else c * (c + 1) / 2 + (n - c) * c
+            pairs = h * 2 * (2 * rank + rd) * seen
+        if layer["mlp"] is not None:
+            per_token += 6 * w * layer["mlp"]["ff"]
+        flops += runs * (per_token * n + pairs)
+    return flops + 2 * w * cfg["vocab"]
+
+
+def budanex_kernels(torch, K, pk, width, heads, kv, dim, ssm_heads, lat_heads, window, tokens=2048,
+                    batch=8):
+    """The design's own kernels alone (median of 20, L2 flushed before each): device time and
+    the fraction of the copy bandwidth their algorithmic bytes reach; for the attention kernels,
+    the same kernel without the design's score modifiers beside it."""
+    dev = "cuda:0"
+    bw = pk["hbm_gbs"] * 1e9
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    bf = torch.bfloat16
+    out = {}
+
+    def timed(name, fn, nbytes):
+        ms = _median_ms(torch, fn, 20, flush)
+        out[name] = {"us": round(ms * 1e3, 1), "frac_of_copy": round(nbytes / (ms * 1e-3) / bw, 4)}
+
+    for label, n, rows in (("prompt", tokens, 1), ("decode", batch, batch)):
+        per = n // rows
+        P_, N = 64, 128
+        inner, ch = ssm_heads * P_, ssm_heads * P_ + 2 * N
+        in_w = 2 * inner + 2 * N + ssm_heads
+        proj = torch.randn(n, in_w, device=dev)
+        conv_w, conv_b = torch.randn(ch, 4, device=dev) * 0.3, torch.zeros(ch, device=dev)
+        conv_state = torch.zeros(rows + 1, ch, 3, device=dev)
+        ssm_state = torch.zeros(rows + 1, ssm_heads, P_, N, device=dev)
+        token_row = torch.arange(rows, dtype=torch.int32, device=dev).repeat_interleave(per)
+        cu = torch.arange(rows + 1, dtype=torch.int32, device=dev) * per
+        slots = torch.arange(rows, dtype=torch.int32, device=dev)
+        u = torch.empty(n, ch, device=dev)
+        y = torch.empty(n, inner, device=dev)
+        g = torch.empty(n, inner, dtype=bf, device=dev)
+        vec = {k_: torch.zeros(ssm_heads, device=dev) for k_ in ("dt", "a", "d")}
+        nw = torch.ones(inner, device=dev)
+        timed(f"conv_silu_{label}", lambda: K.conv_silu(proj, inner, ch, conv_w, conv_b, conv_state,
+                                                         token_row, cu, slots, u, rows, single=(per == 1)),
+              n * ch * 8 + (rows * ch * 3 * 8 if per == 1 else 0))
+        timed(f"ssm_scan_{label}", lambda: K.ssm_scan(u, proj, inner + ch, vec["dt"], vec["a"], vec["d"],
+                                                       ssm_state, cu, slots, y, rows, ssm_heads, P_, N, 1),
+              n * (ch + inner + ssm_heads) * 4 + rows * ssm_heads * P_ * N * 8)
+        timed(f"gated_group_norm_{label}", lambda: K.gated_group_norm(y, proj, 0, nw, g, 1, 1e-5),
+              n * inner * (4 + 4 + 2))
+        # latent attention: prepare, the two per-head products
+        lw = lat_heads * 96 + 128 + lat_heads * 64
+        lproj = torch.randn(n, lw, device=dev)
+        q = torch.empty(n, lat_heads * 96, dtype=bf, device=dev)
+        qa = torch.empty(n, lat_heads * 128, dtype=bf, device=dev)
+        uk = (torch.randn(lat_heads, 96, 64, device=dev) * 0.1).to(bf)
+        uv = (torch.randn(lat_heads, 64, 96, device=dev) * 0.1).to(bf)
+        ol = torch.randn(n, lat_heads * 96, device=dev).to(bf)
+        o = torch.empty(n, lat_heads * 64, dtype=bf, device=dev)
+        timed(f"head_linear_uk_{label}", lambda: K.head_linear(q, uk, qa, x_head=96, x_off=0, y_head=128,
+                                                               tail=32, x_tail_off=64),
+              n * lat_heads * (96 + 128) * 2 + uk.numel() * 2)
+        timed(f"head_linear_uv_gate_{label}", lambda: K.head_linear(ol, uv, o, x_head=96, x_off=0, y_head=64,
+                                                                    gate=lproj, gate_off=lat_heads * 96 + 128),
+              n * lat_heads * (96 * 2 + 64 * 2 + 64 * 4) + uv.numel() * 2)
+    # attention kernels with and without the design's modifiers, over packed keys (a prompt) ...
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    cu1 = torch.tensor([0, tokens], dtype=torch.int32, device=dev)
+    peak = pk["bf16_tflops"] * 1e12
+    for name, nh, nk, hd, vd, win, cap, with_sink in (("attention", heads, kv, dim, dim, 0, 50.0, False),
+                                                       ("latent", lat_heads, 1, 128, 96, window, 0.0, True)):
+        qq = (torch.randn(tokens, nh, hd, device=dev) * 0.5).to(bf)
+        kk = (torch.randn(tokens, nk, hd, device=dev) * 0.5).to(bf)
+        vv = torch.randn(tokens, nk, vd, device=dev).to(bf)
+        oo = torch.empty(tokens, nh * vd, dtype=bf, device=dev)
+        sink = torch.zeros(nh, device=dev) if with_sink else None
+        pairs = tokens * (tokens + 1) / 2 if not win or tokens <= win else win * (win + 1) / 2 + (tokens - win) * win
+        fl = nh * 2 * (hd + vd) * pairs
+        for tag, c, sk in (("", cap, sink), ("_plain_scores", 0.0, None)):
+            ms = _median_ms(torch, lambda: K.sink_attention_mma(
+                qq, kk, vv, cu1, None, None, 0, 0, oo, None, None, 1, tokens, nh, nk, hd, vd, win, 0,
+                with_sink, hd ** -0.5, sink_logit=sk, softcap=c), 20, flush)
+            out[f"{name}_prompt_mma{tag}"] = {"us": round(ms * 1e3, 1),
+                                              "frac_of_product_peak": round(fl / (ms * 1e-3) / peak, 4)}
+        if hd == vd:
+            ms = _median_ms(torch, lambda: K.attention_prefill_tc(qq, kk, vv, cu1, oo, 1, tokens, nh, nk, hd,
+                                                                  win, hd ** -0.5, status), 20, flush)
+            out[f"{name}_prompt_qwen2_tcgen05"] = {"us": round(ms * 1e3, 1),
+                                                   "frac_of_product_peak": round(fl / (ms * 1e-3) / peak, 4)}
+        # ... and single queries over the cache
+        pages = batch * (tokens // 64)
+        kc = (torch.randn(pages, nk, 64, hd, device=dev) * 0.5).to(bf)
+        vc = torch.randn(pages, nk, 64, vd, device=dev).to(bf)
+        table = torch.arange(pages, dtype=torch.int32, device=dev)
+        rows_i = torch.arange(batch, dtype=torch.int32, device=dev)
+        pos = torch.full((batch,), tokens - 1, dtype=torch.int32, device=dev)
+        q1 = (torch.randn(batch, nh, hd, device=dev) * 0.5).to(bf)
+        o1 = torch.empty(batch, nh * vd, dtype=bf, device=dev)
+        seen = min(tokens, win) if win else tokens
+        nbytes = batch * nk * seen * (hd + vd) * 2
+        for tag, c, sk in (("", cap, sink), ("_plain_scores", 0.0, None)):
+            ms = _median_ms(torch, lambda: K.sink_attention_decode(
+                q1, kc, vc, rows_i, pos, table, tokens // 64, 0, o1, None, None, nh, nk, hd, vd, win, 0,
+                with_sink, hd ** -0.5, seen, sink_logit=sk, softcap=c), 20, flush)
+            out[f"{name}_decode_mma{tag}"] = {"us": round(ms * 1e3, 1), "keys": seen,
+                                              "frac_of_copy": round(nbytes / (ms * 1e-3) / bw, 4)}
+    return out
+
+
+def workload_budanex(args) -> int:
+    """Prefill of one 2,048-token prompt and decoding at batch 8 from 2,048-token contexts, for
+    the Budanex design (state-space, latent-attention and attention layers, three of them run
+    twice) and for the Qwen2 decoder at equal width, feed-forward width and layer runs, random
+    weights, bfloat16; and the design's kernels alone."""
+    import torch
+    from minfer_b200.engine.generate import Generator
+    from minfer_b200.kernels import api as K
+    from minfer_b200.model import Model
+    pk, pk_kind = peaks()
+    torch.cuda.set_device(0)
+    steps = max(8, min(args.steps, 128))
+    clocks = ClockSampler()
+    clocks.start()
+    t_all = time.time()
+    sizes = []
+    for name, width, heads, kv, dim, ff, ssm_heads, lat_heads, window in BUDANEX_SIZES:
+        cfg_b = budanex_config(width, heads, kv, dim, ff, ssm_heads, lat_heads, window, FURITAR_VOCAB)
+        cfg_q = dict(CONFIG_7B, vocab_size=FURITAR_VOCAB, hidden_size=width,
+                     num_hidden_layers=BUDANEX_RUNS, num_attention_heads=heads,
+                     num_key_value_heads=kv, intermediate_size=ff, max_position_embeddings=CONTEXT)
+        entry = {"name": name, "width": width, "heads": heads, "kv_heads": kv, "head_size": dim,
+                 "feed_forward": ff, "state_space_heads": ssm_heads, "latent_heads": lat_heads,
+                 "window": window, "layer_runs": BUDANEX_RUNS}
+        for label, cfg in (("budanex", cfg_b), ("qwen2", cfg_q)):
+            model = Model.from_config(cfg, seed=0, dtype="bfloat16", device="cuda:0", make_on="device")
+            gen = Generator(model, max_tokens=BATCH * CONTEXT, max_batch=BATCH)
+            engine = gen.engine
+            g = torch.Generator().manual_seed(2)
+            ids = torch.randint(0, FURITAR_VOCAB, (PROMPT,), generator=g).tolist()
+            ms_prefill = time_prefill(engine, torch, ids, 10)
+            flops = budanex_prefill_flops(cfg, PROMPT) if label == "budanex" else prefill_flops(cfg, PROMPT)
+            ms_step, launched = time_decode(engine, torch, K, BATCH, steps, max(3, args.warmup), PROMPT)
+            ms_med = time_decode.median_ms
+            step_bytes = decode_bytes(model, BATCH, PROMPT + 3 + steps / 2)
+            entry[label] = {
+                "weights_gb": round(model.parameter_bytes() / 1e9, 3),
+                "prefill_tokens_per_s": round(PROMPT * 1e3 / ms_prefill, 1),
+                "prefill_ms": round(ms_prefill, 3),
+                "prefill_frac": round(flops / (ms_prefill * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+                "decode_tokens_per_s": round(BATCH * 1e3 / ms_med, 1),
+                "decode_ms_per_step": round(ms_med, 4), "decode_frac": _frac(step_bytes, ms_med, pk),
+                "decode_launches_per_step": round(launched / steps, 1)}
+            del gen, engine, model
+            torch.cuda.empty_cache()
+        entry["kernels"] = budanex_kernels(torch, K, pk, width, heads, kv, dim, ssm_heads, lat_heads, window)
+        sizes.append(entry)
+    summary = clocks.summary((t_all, time.time()))
+    clocks.stop()
+    print(json.dumps({
+        "workload": "budanex", "impl": "ours", "dtype": "bf16", "data": "synthetic", "n_gpus": 1,
+        "metric": "prefill tokens/s of one 2048-token prompt and decode tokens/s at batch 8 from "
+                  "2048-token contexts, Budanex beside Qwen2 at equal width and layer runs",
+        "unit": "tokens/s", "steps": steps, "prompt_len": PROMPT, "batch": BATCH,
+        "fractions": f"prefill: flops over the {pk_kind} bf16 product peak; decode: bytes of the "
+                     f"weights, the visible cache and the recurrent state over the {pk_kind} copy "
+                     f"bandwidth",
+        "l2": "weights larger than L2 are read every step; kernels alone: L2 flushed before each run",
+        "clocks": summary, "sizes": sizes}))
+    return 0
+
+
 REF_KERNELS = os.path.join(ROOT, "baseline", "_ref", "libref_kernels.so")
 # the reference's checkout, if it sits beside this repository (or where MINFER_REFERENCE_DIR says)
 REF_SOURCE = os.path.join(os.environ.get("MINFER_REFERENCE_DIR",
@@ -660,7 +889,7 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None,
                     help="run fewer layers than the configuration has (both numbers are reported)")
-    ap.add_argument("--workload", default="qwen2-7b", choices=["qwen2-7b", "furitar"],
+    ap.add_argument("--workload", default="qwen2-7b", choices=["qwen2-7b", "furitar", "budanex"],
                     help="qwen2-7b (the default): the headline figure and its points; furitar: "
                          "the Furitar design beside Qwen2 at equal sizes, prefill and decode")
     ap.add_argument("--skip-points", action="store_true",
@@ -679,6 +908,8 @@ def main() -> int:
 
     if args.workload == "furitar":
         return workload_furitar(args)
+    if args.workload == "budanex":
+        return workload_budanex(args)
 
     import torch
     from minfer_b200.engine.generate import Generator

@@ -208,6 +208,11 @@ struct SinkArgs {
     float softcap;            // > 0: s <- softcap * tanh(s / softcap) before the bias
 };
 
+// tanh through one exponential: 1 - 2 / (exp(2y) + 1); exact at both ends (exp -> inf or 0)
+__device__ __forceinline__ float sink_tanh(float y) {
+    return 1.0f - __fdividef(2.0f, __expf(2.0f * y) + 1.0f);
+}
+
 // first visible key of a query at `pos`
 __device__ __forceinline__ int sink_first_key(int pos, int window, int chunk) {
     int lo = window > 0 ? max(0, pos - window + 1) : 0;
@@ -441,6 +446,9 @@ struct SinkMmaArgs {
     int n_heads, n_kv, hd, vd, window, chunk, sink;
     int tab_n;                // entries of the bias table (0: the bias is computed per score)
     float scale_log2;         // scale * log2(e)
+    const float* sink_logit;  // [n_heads] score of the sink, or null for 0
+    float cap_log2;           // soft cap * log2(e); 0: no cap
+    float scale_over_cap;     // scale / soft cap
 };
 
 __device__ __forceinline__ void sm_mma16816(float* d, const uint32_t* a, uint32_t b0, uint32_t b1) {
@@ -554,9 +562,10 @@ sink_attention_mma_kernel(SinkMmaArgs a) {
     };
     load_tile(kt_begin, 0);
 
-    // the sink starts the running maximum at its score, 0
+    // the sink starts the running maximum at its score (0, or the head's learned one)
+    const float sink2 = (a.sink && a.sink_logit) ? a.sink_logit[head] * 1.4426950408889634f : 0.0f;
     float m_r[2], l_r[2] = {0.0f, 0.0f};
-    m_r[0] = m_r[1] = a.sink ? 0.0f : -INFINITY;
+    m_r[0] = m_r[1] = a.sink ? sink2 : -INFINITY;
     float o[VDP / 8][4];
 #pragma unroll
     for (int i = 0; i < VDP / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
@@ -625,7 +634,8 @@ sink_attention_mma_kernel(SinkMmaArgs a) {
                 const int key = key0 + nt * 8 + 2 * t + (e & 1);
                 const int r = e >> 1;
                 const int d = row_p[r] - key;
-                float x = s[nt][e] * a.scale_log2;
+                float x = a.cap_log2 > 0.0f ? a.cap_log2 * sink_tanh(s[nt][e] * a.scale_over_cap)
+                                            : s[nt][e] * a.scale_log2;
                 const bool vis = all_visible || (d >= 0 && key >= row_lo[r]);
                 if (has_bias && vis)
                     x -= a.tab_n > 0 ? tab[d] : r1 * __log2f(fmaf(r2, (float)d, 1.0f));
@@ -687,7 +697,7 @@ sink_attention_mma_kernel(SinkMmaArgs a) {
     for (int r = 0; r < 2; ++r) {
         l_r[r] += __shfl_xor_sync(0xffffffffu, l_r[r], 1);
         l_r[r] += __shfl_xor_sync(0xffffffffu, l_r[r], 2);
-        if (a.sink) l_r[r] += exp2f(-m_r[r]);
+        if (a.sink) l_r[r] += exp2f(sink2 - m_r[r]);
         inv[r] = 1.0f / l_r[r];
     }
 #pragma unroll
@@ -735,8 +745,10 @@ extern "C" int mf_sink_attention_mma(const void* q, const void* k, const void* v
                                      const int* page_table, int table_stride, int ring, void* out,
                                      const float* r1, const float* r2, int n_seqs, int max_new,
                                      int n_heads, int n_kv, int hd, int vd, int window, int chunk,
-                                     int sink, float scale, cudaStream_t stream) {
+                                     int sink, float scale, const float* sink_logit, float softcap,
+                                     cudaStream_t stream) {
     if (n_seqs <= 0 || max_new <= 0) return 0;
+    if (softcap < 0.0f) return MF_ERR_ARGUMENT;
     if (!mf_sink_attention_mma_supported(hd, vd) || n_kv <= 0 || n_heads % n_kv != 0) return MF_ERR_UNSUPPORTED;
     if (n_heads > 65535 || n_seqs > 65535 || window < 0 || chunk < 0) return MF_ERR_UNSUPPORTED;
     if ((page_table == nullptr) != (seq_end == nullptr)) return MF_ERR_ARGUMENT;
@@ -752,6 +764,9 @@ extern "C" int mf_sink_attention_mma(const void* q, const void* k, const void* v
     if (window > 0 && (reach == 0 || window < reach)) reach = window;
     a.tab_n = (r1 != nullptr && reach > 0 && reach <= SM_MAX_TAB) ? reach : 0;
     a.scale_log2 = scale * 1.4426950408889634f;
+    a.sink_logit = sink_logit;
+    a.cap_log2 = softcap * 1.4426950408889634f;
+    a.scale_over_cap = softcap > 0.0f ? scale / softcap : 0.0f;
     const bool paged = page_table != nullptr;
 #define MF_SINK_MMA(H, V) \
     (paged ? launch_sink_mma<H, V, true>(a, n_seqs, max_new, stream) \
@@ -762,8 +777,8 @@ extern "C" int mf_sink_attention_mma(const void* q, const void* k, const void* v
 }
 
 // ------------------------------------------------------------------------------------------
-// Single queries over the paged cache on tensor cores (bfloat16; sizes as above; up to 16
-// query heads per key/value head).
+// Single queries over the paged cache on tensor cores (bfloat16; sizes as above; the query
+// heads of a key/value head in blocks of up to 16).
 //
 // One CTA owns (key split, key/value head, query).  The query heads of the key/value head are
 // the 16 rows of an m16n8k16 MMA, so a key or value is read once for the whole group.  The
@@ -794,6 +809,9 @@ struct SinkDecodeArgs {
     int tiles_per_cta, n_splits;
     int n_bufs;               // buffers a warp has: 2, or 1 when it takes one tile only
     float scale_log2;
+    const float* sink_logit;  // [n_heads] score of the sink, or null for 0
+    float cap_log2;           // soft cap * log2(e); 0: no cap
+    float scale_over_cap;     // scale / soft cap
 };
 
 // a warp copies 32 rows of `d` elements (row r at base + r * d) into its swizzled [32][DP] tile
@@ -821,8 +839,12 @@ __global__ void __launch_bounds__(SD_WARPS * 32) sink_attention_decode_kernel(Si
     constexpr int OS = VDP + 4;                                    // padded row of a warp's output
     extern __shared__ __align__(128) uint8_t sd_smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-    const int split = blockIdx.x, hk = blockIdx.y, row = blockIdx.z;
+    // a group of more than 16 query heads is taken in blocks of 16, a CTA each
     const int G = a.n_heads / a.n_kv;
+    const int gblocks = (G + 15) >> 4;
+    const int split = blockIdx.x, hk = blockIdx.y / gblocks, g0 = (blockIdx.y % gblocks) << 4;
+    const int row = blockIdx.z;
+    const int Gb = min(16, G - g0);
     const int hd = a.hd, vd = a.vd;
     const int b = a.row_seq[row];
     const int pos = a.row_pos[row];
@@ -833,8 +855,8 @@ __global__ void __launch_bounds__(SD_WARPS * 32) sink_attention_decode_kernel(Si
     // this thread's two rows of the product are the group's heads g and g + 8
     float r1v[2] = {0.0f, 0.0f}, r2v[2] = {0.0f, 0.0f};
     if (has_bias) {
-        if (g < G) { r1v[0] = a.r1[hk * G + g]; r2v[0] = a.r2[hk * G + g]; }
-        if (g + 8 < G) { r1v[1] = a.r1[hk * G + g + 8]; r2v[1] = a.r2[hk * G + g + 8]; }
+        if (g < Gb) { r1v[0] = a.r1[hk * G + g0 + g]; r2v[0] = a.r2[hk * G + g0 + g]; }
+        if (g + 8 < Gb) { r1v[1] = a.r1[hk * G + g0 + g + 8]; r2v[1] = a.r2[hk * G + g0 + g + 8]; }
     }
     pdl_wait();
 
@@ -859,9 +881,9 @@ __global__ void __launch_bounds__(SD_WARPS * 32) sink_attention_decode_kernel(Si
     for (int i = 0; i < VDP / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
     uint32_t qa[HDP / 16][4];
     {
-        const __nv_bfloat16* q_lo = a.q + ((long long)row * a.n_heads + hk * G + g) * hd + 2 * t;
+        const __nv_bfloat16* q_lo = a.q + ((long long)row * a.n_heads + hk * G + g0 + g) * hd + 2 * t;
         const __nv_bfloat16* q_hi = q_lo + 8 * (long long)hd;
-        const bool lo_ok = g < G, hi_ok = g + 8 < G;
+        const bool lo_ok = g < Gb, hi_ok = g + 8 < Gb;
 #pragma unroll
         for (int ks = 0; ks < HDP / 16; ++ks) {
             const bool c0 = 16 * ks + 2 * t < hd, c1 = 16 * ks + 8 + 2 * t < hd;
@@ -911,7 +933,8 @@ __global__ void __launch_bounds__(SD_WARPS * 32) sink_attention_decode_kernel(Si
                 const int key = key0 + nt * 8 + 2 * t + (e & 1);
                 const int d = pos - key;
                 const bool vis = d >= 0 && key >= lo;
-                float x = s[nt][e] * a.scale_log2;
+                float x = a.cap_log2 > 0.0f ? a.cap_log2 * sink_tanh(s[nt][e] * a.scale_over_cap)
+                                            : s[nt][e] * a.scale_log2;
                 if (has_bias && vis) x -= r1v[e >> 1] * __log2f(fmaf(r2v[e >> 1], (float)d, 1.0f));
                 s[nt][e] = vis ? x : -INFINITY;
             }
@@ -981,7 +1004,7 @@ __global__ void __launch_bounds__(SD_WARPS * 32) sink_attention_decode_kernel(Si
         ml_s[(warp * 16 + g + 8) * 2] = m_r[1]; ml_s[(warp * 16 + g + 8) * 2 + 1] = l_r[1];
     }
     __syncthreads();
-    for (int idx = tid; idx < G * VDP; idx += SD_WARPS * 32) {
+    for (int idx = tid; idx < Gb * VDP; idx += SD_WARPS * 32) {
         const int r = idx / VDP, d = idx - r * VDP;
         if (d >= vd) continue;
         float m = -INFINITY;
@@ -997,17 +1020,18 @@ __global__ void __launch_bounds__(SD_WARPS * 32) sink_attention_decode_kernel(Si
                 acc = fmaf(o_s[((size_t)w * 16 + r) * OS + d], f, acc);
             }
         }
-        const int head = hk * G + r;
+        const int head = hk * G + g0 + r;
         if (a.n_splits > 1) {
             float* part = a.partial + (((size_t)row * a.n_heads + head) * a.n_splits + split) * (vd + 2);
             if (d == 0) { part[0] = m; part[1] = l; }
             part[2 + d] = acc;
         } else {
             float mf = m;
-            if (a.sink) {                                         // the sink: a key of score 0, no value
-                mf = fmaxf(m, 0.0f);
+            if (a.sink) {                                         // the sink: a key without a value
+                const float sink2 = a.sink_logit ? a.sink_logit[head] * 1.4426950408889634f : 0.0f;
+                mf = fmaxf(m, sink2);
                 const float f = m > -INFINITY ? exp2f(m - mf) : 0.0f;
-                l = l * f + exp2f(-mf);
+                l = l * f + exp2f(sink2 - mf);
                 acc *= f;
             }
             a.out[((size_t)row * a.n_heads + head) * vd + d] = __float2bfloat16_rn(acc / l);
@@ -1018,14 +1042,16 @@ __global__ void __launch_bounds__(SD_WARPS * 32) sink_attention_decode_kernel(Si
 // merges the splits of one (query, head) in split order and adds the sink
 __global__ void sink_decode_combine_kernel(const float* __restrict__ partial,
                                            __nv_bfloat16* __restrict__ out, int n_splits, int vd,
-                                           int sink) {
+                                           int sink, const float* __restrict__ sink_logit,
+                                           int n_heads) {
     pdl_prologue();
     const size_t rh = blockIdx.x;
     const size_t stride = (size_t)(vd + 2);
     const float* p = partial + rh * n_splits * stride;
-    float m = sink ? 0.0f : -INFINITY;
+    const float sink2 = (sink && sink_logit) ? sink_logit[rh % n_heads] * 1.4426950408889634f : 0.0f;
+    float m = sink ? sink2 : -INFINITY;
     for (int c = 0; c < n_splits; ++c) m = fmaxf(m, p[c * stride]);
-    float l = sink ? exp2f(-m) : 0.0f;
+    float l = sink ? exp2f(sink2 - m) : 0.0f;
     for (int c = 0; c < n_splits; ++c) {
         const float mc = p[c * stride];
         if (mc > -INFINITY) l = fmaf(p[c * stride + 1], exp2f(mc - m), l);
@@ -1042,7 +1068,8 @@ __global__ void sink_decode_combine_kernel(const float* __restrict__ partial,
 }
 
 // How the keys of single queries are cut: (tiles of 32 keys per CTA, splits), from the sizes
-// only.  `reach_keys`: the most keys a query sees (its reach, or the longest sequence).
+// only.  `n_kv`: key/value heads times the blocks of 16 query heads on each.  `reach_keys`: the
+// most keys a query sees (its reach, or the longest sequence).
 extern "C" int mf_sink_decode_plan(int rows, int n_kv, int reach_keys, int* tiles_per_cta,
                                    int* n_splits) {
     const int n_tiles = reach_keys / SD_KEYS + 2;                  // the range need not start on a tile
@@ -1072,7 +1099,8 @@ static int launch_sink_decode(const SinkDecodeArgs& a, int rows, cudaStream_t st
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    mf_launch(sink_attention_decode_kernel<HDP, VDP>, dim3(a.n_splits, a.n_kv, rows),
+    const int gblocks = (a.n_heads / a.n_kv + 15) / 16;
+    mf_launch(sink_attention_decode_kernel<HDP, VDP>, dim3(a.n_splits, a.n_kv * gblocks, rows),
               dim3(SD_WARPS * 32), (size_t)smem, stream, a);
     return MF_LAUNCH_CHECK();
 }
@@ -1087,10 +1115,13 @@ extern "C" int mf_sink_attention_decode(const void* q, const void* k_cache, cons
                                         void* out, float* partial, const float* r1,
                                         const float* r2, int rows, int n_heads, int n_kv, int hd,
                                         int vd, int window, int chunk, int sink, float scale,
-                                        int reach_keys, cudaStream_t stream) {
+                                        int reach_keys, const float* sink_logit, float softcap,
+                                        cudaStream_t stream) {
     if (rows <= 0) return 0;
+    if (softcap < 0.0f) return MF_ERR_ARGUMENT;
     if (!mf_sink_attention_mma_supported(hd, vd) || n_kv <= 0 || n_heads % n_kv != 0) return MF_ERR_UNSUPPORTED;
-    if (n_heads / n_kv > 16 || n_kv > 65535 || rows > 65535) return MF_ERR_UNSUPPORTED;
+    const int head_blocks = n_kv * ((n_heads / n_kv + 15) / 16);      // CTAs per (split, query)
+    if (head_blocks > 65535 || rows > 65535) return MF_ERR_UNSUPPORTED;
     if (page_table == nullptr || window < 0 || chunk < 0) return MF_ERR_ARGUMENT;
     SinkDecodeArgs a;
     a.q = (const __nv_bfloat16*)q; a.k = (const __nv_bfloat16*)k_cache;
@@ -1100,7 +1131,10 @@ extern "C" int mf_sink_attention_decode(const void* q, const void* k_cache, cons
     a.n_heads = n_heads; a.n_kv = n_kv; a.hd = hd; a.vd = vd; a.window = window; a.chunk = chunk;
     a.sink = sink ? 1 : 0;
     a.scale_log2 = scale * 1.4426950408889634f;
-    mf_sink_decode_plan(rows, n_kv, reach_keys, &a.tiles_per_cta, &a.n_splits);
+    a.sink_logit = sink_logit;
+    a.cap_log2 = softcap * 1.4426950408889634f;
+    a.scale_over_cap = softcap > 0.0f ? scale / softcap : 0.0f;
+    mf_sink_decode_plan(rows, head_blocks, reach_keys, &a.tiles_per_cta, &a.n_splits);
     a.n_bufs = a.tiles_per_cta > SD_WARPS ? 2 : 1;
     if (a.n_splits > 1 && partial == nullptr) return MF_ERR_ARGUMENT;
     int e;
@@ -1110,6 +1144,7 @@ extern "C" int mf_sink_attention_decode(const void* q, const void* k_cache, cons
                       : launch_sink_decode<128, 128>(a, rows, stream);
     if (e || a.n_splits == 1) return e;
     mf_launch_ex(false, sink_decode_combine_kernel, dim3(rows * n_heads), dim3(vd <= 64 ? 64 : 128), 0,
-                 stream, (const float*)partial, (__nv_bfloat16*)out, a.n_splits, vd, a.sink);
+                 stream, (const float*)partial, (__nv_bfloat16*)out, a.n_splits, vd, a.sink, sink_logit,
+                 n_heads);
     return MF_LAUNCH_CHECK();
 }

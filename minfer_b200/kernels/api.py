@@ -140,12 +140,12 @@ def _sig_attention_sink(lib: ctypes.CDLL) -> None:
 
     lib.mf_sink_attention_mma_supported.argtypes = [c_int, c_int]
     lib.mf_sink_attention_mma.argtypes = ([c_void_p] * 6 + [c_int, c_int] + [c_void_p] * 3 +
-                                          [c_int] * 9 + [c_float, c_void_p])
+                                          [c_int] * 9 + [c_float, c_void_p, c_float, c_void_p])
 
 
     lib.mf_sink_decode_plan.argtypes = [c_int, c_int, c_int, c_void_p, c_void_p]
     lib.mf_sink_attention_decode.argtypes = ([c_void_p] * 6 + [c_int, c_int] + [c_void_p] * 4 +
-                                             [c_int] * 8 + [c_float, c_int, c_void_p])
+                                             [c_int] * 8 + [c_float, c_int, c_void_p, c_float, c_void_p])
 
 
 def _sig_sampling(lib: ctypes.CDLL) -> None:
@@ -1023,7 +1023,8 @@ def sink_attention_mma(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seq
                        table_stride: int, ring: int, out: torch.Tensor, r1: Optional[torch.Tensor],
                        r2: Optional[torch.Tensor], n_rows: int, max_row_tokens: int, n_heads: int,
                        n_kv: int, head_dim: int, value_dim: int, window: int, chunk: int, sink: bool,
-                       scale: float) -> None:
+                       scale: float, sink_logit: Optional[torch.Tensor] = None,
+                       softcap: float = 0.0) -> None:
     """The step's packed queries (sequence b brings tokens cu_seqlens[b] .. cu_seqlens[b+1]-1)
     on tensor cores.  ``page_table`` None: ``k``, ``v`` are the step's own packed rows and every
     sequence starts at position 0; else they are the cache and sequence b ends at
@@ -1037,7 +1038,7 @@ def sink_attention_mma(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seq
         _i32(seq_end, "seq_end"), _i32(page_table, "page_table"), int(table_stride), int(ring),
         _ptr(out, "out"), _f32(r1, "r1"), _f32(r2, "r2"), int(n_rows), int(max_row_tokens), n_heads,
         n_kv, head_dim, value_dim, int(window), int(chunk), 1 if sink else 0, float(scale),
-        _stream()), "sink_attention_mma")
+        _f32(sink_logit, "sink_logit"), float(softcap), _stream()), "sink_attention_mma")
 
 
 def sink_attention_tc_supported(dtype: torch.dtype, head_dim: int, value_dim: int) -> bool:
@@ -1088,16 +1089,18 @@ def sink_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch
                           table_stride: int, ring: int, out: torch.Tensor,
                           r1: Optional[torch.Tensor], r2: Optional[torch.Tensor], n_heads: int,
                           n_kv: int, head_dim: int, value_dim: int, window: int, chunk: int,
-                          sink: bool, scale: float, reach_keys: int) -> None:
+                          sink: bool, scale: float, reach_keys: int,
+                          sink_logit: Optional[torch.Tensor] = None, softcap: float = 0.0) -> None:
     """Every row of ``q`` a query at its own position over the paged cache, on tensor cores
-    (bfloat16, up to 16 query heads per key/value head).  ``reach_keys``: the most keys a query
+    (bfloat16; the query heads of a key/value head in blocks of up to 16).  ``reach_keys``: the most keys a query
     sees (its chunk or window, or the longest sequence's length)."""
     rows = q.shape[0]
     if q.dtype != torch.bfloat16 or out.shape != (rows, n_heads * value_dim):
         raise KernelError("sink_attention_decode: bfloat16 only, out [rows, heads * value size]")
     if (r1 is None) != (r2 is None):
         raise KernelError("sink_attention_decode: inconsistent arguments")
-    _, splits = sink_decode_plan(rows, n_kv, int(reach_keys))
+    head_blocks = n_kv * ((n_heads // n_kv + 15) // 16)
+    _, splits = sink_decode_plan(rows, head_blocks, int(reach_keys))
     partial = None
     if splits > 1:
         partial = torch.empty(rows * n_heads * splits * (value_dim + 2), dtype=torch.float32,
@@ -1107,7 +1110,8 @@ def sink_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch
         _i32(row_pos, "row_pos"), _i32(page_table, "page_table"), int(table_stride), int(ring),
         _ptr(out, "out"), _f32(partial, "partial"), _f32(r1, "r1"), _f32(r2, "r2"), rows, n_heads,
         n_kv, head_dim, value_dim, int(window), int(chunk), 1 if sink else 0, float(scale),
-        int(reach_keys), _stream()), "sink_attention_decode", 2 if splits > 1 else 1)
+        int(reach_keys), _f32(sink_logit, "sink_logit"), float(softcap), _stream()),
+        "sink_attention_decode", 2 if splits > 1 else 1)
 
 
 def sampler_state_ints() -> int:

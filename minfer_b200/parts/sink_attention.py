@@ -81,12 +81,11 @@ def scored_attention(spec: ScoreSpec, q: torch.Tensor, k_step: Optional[torch.Te
     act = q.dtype
     own_kv = ctx.from_start
     r1, r2 = spec.r1, spec.r2
-    # the tensor-core kernels take neither a soft cap nor a learned score of the sink
-    plain_scores = spec.softcap == 0.0 and spec.sink_logit is None
-    tensor_cores = (plain_scores and K.sink_attention_mma_supported(act, hd, vd)
-                    and not FORCE_GENERIC)
-    # prompts: the tcgen05 kernel where keys and values have one size it takes, else mma.sync
-    tcgen05 = (tensor_cores and PROMPT_KERNEL != "mma"
+    cap, sl = spec.softcap, spec.sink_logit
+    tensor_cores = K.sink_attention_mma_supported(act, hd, vd) and not FORCE_GENERIC
+    # prompts: the tcgen05 kernel where keys and values have one size it takes (it knows neither
+    # a soft cap nor a learned score of the sink), else mma.sync
+    tcgen05 = (tensor_cores and PROMPT_KERNEL != "mma" and cap == 0.0 and sl is None
                and K.sink_attention_tc_supported(act, hd, vd))
     if own_kv and tcgen05:
         K.sink_attention_tc(q, k_step, v_step, ctx.cu_seqlens, None, None, 0, 0, o, r1, r2,
@@ -96,7 +95,7 @@ def scored_attention(spec: ScoreSpec, q: torch.Tensor, k_step: Optional[torch.Te
     if own_kv and tensor_cores:
         K.sink_attention_mma(q, k_step, v_step, ctx.cu_seqlens, None, None, 0, 0, o, r1, r2,
                              ctx.n_rows, ctx.max_row_tokens, nh, nk, hd, vd, spec.window,
-                             spec.chunk, spec.sink, spec.scale)
+                             spec.chunk, spec.sink, spec.scale, sink_logit=sl, softcap=cap)
         return
     if own_kv:
         K.sink_attention_packed(q, k_step, v_step, ctx.token_row, ctx.positions, ctx.cu_seqlens, o,
@@ -120,14 +119,14 @@ def scored_attention(spec: ScoreSpec, q: torch.Tensor, k_step: Optional[torch.Te
         K.sink_attention_mma(q, cache.k, cache.v, ctx.cu_seqlens, ctx.seq_end, cache.page_table,
                              cache.table_stride, cache.ring, o, r1, r2, ctx.n_rows,
                              ctx.max_row_tokens, nh, nk, hd, vd, spec.window, spec.chunk,
-                             spec.sink, spec.scale)
+                             spec.sink, spec.scale, sink_logit=sl, softcap=cap)
         return
-    if tensor_cores and nh // nk <= 16:
+    if tensor_cores:
         # single queries: the heads of a key/value head are the rows of the product
         K.sink_attention_decode(q, cache.k, cache.v, ctx.token_row, ctx.positions,
                                 cache.page_table, cache.table_stride, cache.ring, o, r1, r2, nh,
                                 nk, hd, vd, spec.window, spec.chunk, spec.sink, spec.scale,
-                                reach if reach > 0 else ctx.max_end)
+                                reach if reach > 0 else ctx.max_end, sink_logit=sl, softcap=cap)
         return
     K.sink_attention_paged(q, cache.k, cache.v, ctx.token_row, ctx.positions, cache.page_table,
                            cache.table_stride, cache.ring, o, r1, r2, nh, nk, hd, vd, spec.window,

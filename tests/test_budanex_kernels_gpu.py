@@ -84,6 +84,35 @@ def test_attention_kernel_with_a_key_that_stands_out(dtype, window, standout):
                                softcap=25.0)
         err = float((out2.cpu().to(torch.float64).view(len(live), H, Dv) - want[sel]).abs().max())
         assert err < _tol(dtype) * float(want.abs().max()), (ring, err)
+        if dtype != torch.bfloat16:
+            continue
+        # the tensor-core kernels: single queries over the pages ...
+        out3 = torch.empty((len(live), H * Dv), dtype=dtype, device=DEV)
+        K.sink_attention_decode(qd[sel].contiguous(), kc, vc, row_seq[:len(live)].contiguous(),
+                                row_pos[sel].contiguous(), table, table.numel(), ring, out3, None,
+                                None, H, G, D, Dv, window, 0, True, 0.4, window if window else n,
+                                sink_logit=sink_d, softcap=25.0)
+        err = float((out3.cpu().to(torch.float64).view(len(live), H, Dv) - want[sel]).abs().max())
+        assert err < _tol(dtype) * float(want.abs().max()), ("decode", ring, err)
+        # ... and the sequence's last 50 tokens as one portion over the pages
+        tail = list(range(n - 50, n))
+        want_tail = P.scored_attention(q[tail], k, v, tail, 0.4, window, 25.0, sink)
+        out4 = torch.empty((50, H * Dv), dtype=dtype, device=DEV)
+        K.sink_attention_mma(q[tail].to(dtype).to(DEV).contiguous(), kc, vc,
+                             torch.tensor([0, 50], dtype=torch.int32, device=DEV),
+                             torch.tensor([n], dtype=torch.int32, device=DEV), table, table.numel(),
+                             ring, out4, None, None, 1, 50, H, G, D, Dv, window, 0, True, 0.4,
+                             sink_logit=sink_d, softcap=25.0)
+        err = float((out4.cpu().to(torch.float64).view(50, H, Dv) - want_tail).abs().max())
+        assert err < _tol(dtype) * float(want.abs().max()), ("portion", ring, err)
+    if dtype == torch.bfloat16:
+        # the whole prompt over its own packed keys on tensor cores
+        out5 = torch.empty((n, H * Dv), dtype=dtype, device=DEV)
+        K.sink_attention_mma(q.to(dtype).to(DEV).contiguous(), k.to(dtype).to(DEV), v.to(dtype).to(DEV),
+                             cu, None, None, 0, 0, out5, None, None, 1, n, H, G, D, Dv, window, 0,
+                             True, 0.4, sink_logit=sink_d, softcap=25.0)
+        err = float((out5[rows].cpu().to(torch.float64).view(len(rows), H, Dv) - want).abs().max())
+        assert err < _tol(dtype) * float(want.abs().max()), ("prompt", err)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -284,3 +313,28 @@ def test_soft_cap_and_stream_add():
     hd = h.to(DEV)
     K.add_stream(hd, None, v.float().to(DEV))
     assert torch.allclose(hd.cpu(), h + v.float(), atol=1e-6)
+
+
+@pytest.mark.parametrize("heads, kv", [(40, 1), (34, 2), (16, 1), (17, 1)])
+def test_single_queries_with_many_heads_on_one_key_head(heads, kv):
+    """The tensor-core kernel for single queries takes a key/value head's query heads in blocks
+    of 16: groups of 40, 17 (a block of one head) and exactly 16."""
+    from minfer_b200.kernels import api as K
+    torch.manual_seed(heads)
+    n, D, Dv, window = 300, 32, 16, 150
+    dtype = torch.bfloat16
+    q = (torch.randn(n, heads, D, dtype=torch.float64) * 0.7).to(dtype).double()
+    k = (torch.randn(n, kv, D, dtype=torch.float64) * 0.7).to(dtype).double()
+    v = torch.randn(n, kv, Dv, dtype=torch.float64).to(dtype).double()
+    sink = torch.linspace(-2.0, 2.0, heads, dtype=torch.float64)
+    rows = [n - 1, 200, 149, 150, 3]
+    want = P.scored_attention(q[rows], k, v, rows, 0.3, window, 0.0, sink)
+    kc, vc, table = _paged(k, v, dtype)
+    out = torch.empty((len(rows), heads * Dv), dtype=dtype, device=DEV)
+    K.sink_attention_decode(q[rows].to(dtype).to(DEV).contiguous(), kc, vc,
+                            torch.zeros(len(rows), dtype=torch.int32, device=DEV),
+                            torch.tensor(rows, dtype=torch.int32, device=DEV), table, table.numel(), 0,
+                            out, None, None, heads, kv, D, Dv, window, 0, True, 0.3, window,
+                            sink_logit=sink.float().to(DEV))
+    err = float((out.cpu().double().view(len(rows), heads, Dv) - want).abs().max())
+    assert err < 2e-2 * float(want.abs().max()), err

@@ -158,6 +158,7 @@ class GroupKey:
     head_dim: int
     window: int          # 0: linear
     value_dim: int = 0   # width of a value vector if it differs from head_dim (0: the same)
+    shared_values: bool = False      # values are the keys: one tensor serves as both
 
 
 class CacheGroup:
@@ -182,10 +183,15 @@ class CacheGroup:
         v_shape = shape[:-1] + (key.value_dim or key.head_dim,)
         # zeros, once: a page's unwritten positions are masked by length but still multiplied
         # by a zero weight in the tensor-core kernels, so they must never hold NaN or Inf
-        self._guarded = [Guarded(shape, dtype, device, f"keys of cache group {key}"),
-                         Guarded(v_shape, dtype, device, f"values of cache group {key}")]
+        self._guarded = [Guarded(shape, dtype, device, f"keys of cache group {key}")]
         self.k = self._guarded[0].tensor
-        self.v = self._guarded[1].tensor
+        if key.shared_values:
+            if key.value_dim not in (0, key.head_dim):
+                raise CacheError("values that are the keys cannot have another width")
+            self.v = self.k
+        else:
+            self._guarded.append(Guarded(v_shape, dtype, device, f"values of cache group {key}"))
+            self.v = self._guarded[1].tensor
         self._index = {e: i for i, e in enumerate(self.entries)}
 
     def max_new_positions(self) -> Optional[int]:
@@ -348,7 +354,8 @@ class Cache:
 
     def bytes(self) -> int:
         """Bytes of key/value storage that sequences can hold (the spare pages not counted)."""
-        return sum(2 * g.k[:, :g.n_pages].numel() * g.k.element_size() for g in self.groups)
+        return sum((g.k[:, :g.n_pages].numel() + (0 if g.key.shared_values else g.v[:, :g.n_pages].numel()))
+                   * g.k.element_size() for g in self.groups)
 
     def free_pages(self) -> List[int]:
         return [g.pool.n_free() for g in self.groups]

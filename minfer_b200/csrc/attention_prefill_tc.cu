@@ -70,6 +70,11 @@ struct FaArgs {
     int tab_n;                // entries of the bias table in shared memory (0: computed per score)
     const float* r1;          // [n_heads] or null
     const float* r2;
+    //   two more, both optional: a soft cap, s <- cap tanh(s / cap) on (q . k) * scale before the
+    //   bias, held in units of the raw score (cap_raw = cap / scale, inv_cap_raw = scale / cap;
+    //   0: none); a learned score of the sink per head instead of 0
+    float cap_raw, inv_cap_raw;
+    const float* sink_logit;  // [n_heads] or null
 };
 
 #define FA_TAB_PAD 256        // zeros on either side of the bias table (indices of masked scores)
@@ -433,8 +438,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const uint32_t s_addr = lane_addr + (uint32_t)(TM_S + t * 128);
         const uint32_t o_addr = lane_addr + (uint32_t)(TM_O + t * 128);
         const int kb_t = t ? kb[1] : kb[0], ke_t = t ? ke[1] : ke[0];
-        // the sink is a key of score 0: it starts the running maximum
-        float m = (MOD && a.sink) ? 0.0f : -INFINITY, l = 0.0f;
+        // the sink is a key without a value: its score (0 or the head's learned one, in units of
+        // the raw score) starts the running maximum
+        const float sink_raw = (MOD && a.sink && a.sink_logit)
+            ? a.sink_logit[head] * 1.4426950408889634f / a.scale_log2 : 0.0f;
+        float m = (MOD && a.sink) ? sink_raw : -INFINITY, l = 0.0f;
         const int row_lo = MOD ? fa_first_key(qpos, 0, a.chunk) : 0;              // chunk's first key
         const int warp_lo = MOD ? fa_first_key(wpos + 31, 0, a.chunk) : 0;
         bool ok = true;
@@ -453,6 +461,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
             for (int c0 = 0; c0 < FA_KEYS; c0 += 32) fa_ld32(s_addr + (uint32_t)c0, sr + c0);
             fa_wait_ld();
+            if (MOD && a.cap_raw > 0.0f) {
+                // the soft cap, in units of the raw score (tanh.approx: 2^-11 of the score)
+#pragma unroll
+                for (int i = 0; i < FA_KEYS; ++i) {
+                    float th;
+                    asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(__uint_as_float(sr[i]) * a.inv_cap_raw));
+                    sr[i] = __float_as_uint(a.cap_raw * th);
+                }
+            }
             if (MOD && has_bias) {
                 // the distance bias, in units of the raw score (what is masked below may read the
                 // zeros around the table)
@@ -545,7 +562,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         // ---- the result: O / sum -------------------------------------------------------------
         if (ok && ke_t > kb_t && fa_wait(fa_smem(&o_done[t]), 0u, abort_flag)) {
             fa_fence_after();
-            if (MOD && a.sink) l += exp2f(-m * a.scale_log2);         // m >= 0 from the start
+            if (MOD && a.sink) l += exp2f((sink_raw - m) * a.scale_log2);   // m >= the sink's score from the start
             const float inv = 1.0f / l;
             __nv_bfloat16* o = a.out + ((long long)(tok0 + qrow) * a.n_heads + head) * HD;
 #pragma unroll 1
@@ -706,9 +723,10 @@ extern "C" int mf_sink_attention_tc(const void* q, const void* k, const void* v,
                                     const int* seq_end, const int* page_table, int table_stride, int ring,
                                     void* out, const float* r1, const float* r2, int n_tokens, int n_seqs,
                                     int max_len, int n_heads, int n_kv, int hd, int window, int chunk,
-                                    int sink, float scale, long long cache_pages, unsigned* status,
-                                    cudaStream_t stream) {
+                                    int sink, float scale, long long cache_pages, const float* sink_logit,
+                                    float softcap, unsigned* status, cudaStream_t stream) {
     if (n_seqs <= 0 || max_len <= 0 || n_tokens <= 0) return 0;
+    if (softcap < 0.0f) return MF_ERR_ARGUMENT;
     if ((hd != 64 && hd != 128) || n_kv <= 0 || n_heads % n_kv != 0) return MF_ERR_UNSUPPORTED;
     if (n_seqs > 65535 || (max_len + FA_CTA_Q - 1) / FA_CTA_Q > 65535) return MF_ERR_UNSUPPORTED;
     if (((uintptr_t)q & 15) || ((uintptr_t)k & 15) || ((uintptr_t)v & 15) || ((uintptr_t)out & 15))
@@ -731,6 +749,9 @@ extern "C" int mf_sink_attention_tc(const void* q, const void* k, const void* v,
     a.scale_log2 = scale * 1.4426950408889634f;
     a.seq_end = seq_end; a.page_table = page_table; a.table_stride = table_stride; a.ring = ring;
     a.chunk = chunk; a.sink = sink ? 1 : 0; a.r1 = r1; a.r2 = r2;
+    a.sink_logit = sink_logit;
+    a.cap_raw = softcap > 0.0f ? softcap / scale : 0.0f;
+    a.inv_cap_raw = softcap > 0.0f ? scale / softcap : 0.0f;
     int reach = chunk;
     if (window > 0 && (reach == 0 || window < reach)) reach = window;
     a.tab_n = (r1 != nullptr && reach > 0 && reach <= FA_TAB_MAX) ? reach : 0;

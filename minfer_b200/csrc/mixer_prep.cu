@@ -9,7 +9,8 @@
 //                  or (2i, 2i + 1), angle position * inv_freq[i] formed in float64, cosine and
 //                  sine times `rot_mag`), and writes q, the step's k and v, and the cache's pages.
 //                  Values are a segment of their own (n_kv heads of vw) or, with v_from_k, the
-//                  first vw elements of each prepared key head (a latent shared by both).
+//                  first vw elements of each prepared key head (a latent shared by both); the
+//                  places for such values may be null, for a caller that reads them from the keys.
 //   head_linear    y[t][h][j] = sum_d W[h][j][d] x[t][h][x_off + d] for every head h, optionally
 //                  times sigmoid(gate[t][h * J + j]), optionally followed by a copy of `tail`
 //                  elements x[t][h][x_tail_off ..] behind the J outputs.  float32 accumulation.
@@ -131,7 +132,7 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(PrepArgs a) {
             ((T*)a.k_cache)[(((size_t)page * a.n_kv + hk) * MF_PAGE + in_page) * a.kw + d] = y;
         if (a.v_from_k && d < a.vw) {
             if (a.v_out) ((T*)a.v_out)[((size_t)t * a.n_kv + hk) * a.vw + d] = y;
-            if (page >= 0)
+            if (page >= 0 && a.v_cache)
                 ((T*)a.v_cache)[(((size_t)page * a.n_kv + hk) * MF_PAGE + in_page) * a.vw + d] = y;
         }
     }
@@ -154,7 +155,8 @@ extern "C" int mf_qk_prepare(const PrepArgs* args, int n_tokens, int dtype, cuda
     if (a.rot_dims < 0 || (a.rot_dims & 1) || (a.rot_dims > 0 && a.inv_freq == nullptr)) return MF_ERR_ARGUMENT;
     if (a.q_rot_off + a.rot_dims > a.qw || a.k_rot_off + a.rot_dims > a.kw) return MF_ERR_ARGUMENT;
     if (a.q_norm_n > a.n_heads * a.qw || a.k_norm_n > a.n_kv * a.kw) return MF_ERR_ARGUMENT;
-    if ((a.k_cache == nullptr) != (a.v_cache == nullptr)) return MF_ERR_ARGUMENT;
+    // (values taken from the keys need no place of their own: the caller may use the keys)
+    if (!a.v_from_k && (a.k_cache == nullptr) != (a.v_cache == nullptr)) return MF_ERR_ARGUMENT;
     if (a.k_cache != nullptr && a.page_table == nullptr) return MF_ERR_ARGUMENT;
     if (a.v_from_k && a.vw > a.kw) return MF_ERR_ARGUMENT;
     // a rotated pair must lie wholly inside or wholly outside the normed stretch of its segment

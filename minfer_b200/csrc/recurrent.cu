@@ -9,6 +9,8 @@
 //   conv_silu         u[t][c] = silu(bias[c] + sum_j taps[c][j] * in[t - (T - 1 - j)][c]) over the
 //                     channels c of x | B | C; inputs before the row's first token come from the
 //                     slot's state (the last T - 1 inputs, oldest first; zeros for a new sequence)
+//                     (a thread per token and channel for single tokens; for longer rows a
+//                     thread walks a run of tokens with the history in registers)
 //   conv_state        the state after the step (a kernel of its own unless every row brings one
 //                     token: a row's first block reads what its last would write)
 //   ssm_scan          per (row, head): dt = softplus(raw + dt_bias), a = exp(-exp(A_log) dt),
@@ -73,6 +75,56 @@ conv_silu_kernel(const float* __restrict__ proj, long long in_width, int x_off, 
     }
 }
 
+// Steps that bring more than one token a row: a thread owns a channel over a run of RC_CONV_TB
+// packed tokens and keeps the last taps - 1 inputs in registers, so every input is read once;
+// at the run's first token and at every first token of a row the history is fetched again (from
+// the row's earlier tokens or from the slot's state).
+#define RC_CONV_TB 16
+__global__ void __launch_bounds__(256)
+conv_silu_run_kernel(const float* __restrict__ proj, long long in_width, int x_off, int channels,
+                     int taps, const float* __restrict__ w, const float* __restrict__ bias,
+                     const float* __restrict__ state, const int* __restrict__ token_row,
+                     const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
+                     float* __restrict__ out, int n_tokens) {
+    pdl_launch_dependents();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= channels) return;
+    const int t_lo = blockIdx.y * RC_CONV_TB, t_hi = min(n_tokens, t_lo + RC_CONV_TB);
+    float wt[RC_MAX_TAPS];
+#pragma unroll
+    for (int j = 0; j < RC_MAX_TAPS; ++j) wt[j] = j < taps ? w[(size_t)c * taps + j] : 0.0f;
+    const float bv = bias ? bias[c] : 0.0f;
+    pdl_wait();
+    float hist[RC_MAX_TAPS];                     // hist[j]: the input taps - 1 - j tokens back
+#pragma unroll
+    for (int j = 0; j < RC_MAX_TAPS; ++j) hist[j] = 0.0f;
+    for (int t = t_lo; t < t_hi; ++t) {
+        const int b = token_row[t];
+        const int i = t - cu_seqlens[b];
+        if (t == t_lo || i == 0) {
+            const float* st = state + ((size_t)slots[b] * channels + c) * (taps - 1);
+#pragma unroll
+            for (int j = 0; j < RC_MAX_TAPS; ++j) {
+                if (j < taps - 1) {
+                    const int s = i - (taps - 1 - j);
+                    hist[j] = s >= 0 ? proj[(size_t)(t - (i - s)) * in_width + x_off + c]
+                                     : st[taps - 1 + s];
+                }
+            }
+        }
+        const float v = proj[(size_t)t * in_width + x_off + c];
+        float acc = bv;
+#pragma unroll
+        for (int j = 0; j < RC_MAX_TAPS; ++j)
+            if (j < taps - 1) acc = fmaf(wt[j], hist[j], acc);
+        acc = fmaf(wt[taps - 1], v, acc);
+        out[(size_t)t * channels + c] = rc_silu(acc);
+#pragma unroll
+        for (int j = 0; j < RC_MAX_TAPS - 1; ++j)
+            if (j < taps - 1) hist[j] = j + 1 < taps - 1 ? hist[j + 1] : v;
+    }
+}
+
 // one thread per (row, channel): the state after the row's tokens
 __global__ void __launch_bounds__(256)
 conv_state_kernel(const float* __restrict__ proj, long long in_width, int x_off, int channels,
@@ -107,9 +159,14 @@ extern "C" int mf_conv_silu(const float* proj, long long in_width, int x_off, in
     if (n_tokens <= 0) return 0;
     if (taps < 1 || taps > RC_MAX_TAPS || channels < 1) return MF_ERR_UNSUPPORTED;
     const long long total = (long long)n_tokens * channels;
-    mf_launch(conv_silu_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, proj,
-              in_width, x_off, channels, taps, w, bias, state, token_row, cu_seqlens, slots, out,
-              total, single);
+    if (single || n_tokens < RC_CONV_TB)
+        mf_launch(conv_silu_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, proj,
+                  in_width, x_off, channels, taps, w, bias, state, token_row, cu_seqlens, slots, out,
+                  total, single);
+    else
+        mf_launch(conv_silu_run_kernel, dim3((channels + 255) / 256, (n_tokens + RC_CONV_TB - 1) / RC_CONV_TB),
+                  dim3(256), 0, stream, proj, in_width, x_off, channels, taps, w, bias, (const float*)state,
+                  token_row, cu_seqlens, slots, out, n_tokens);
     if (!single && taps > 1) {
         const long long per_row = (long long)n_rows * channels;
         mf_launch(conv_state_kernel, dim3((unsigned)((per_row + 255) / 256)), dim3(256), 0, stream,
@@ -121,12 +178,16 @@ extern "C" int mf_conv_silu(const float* proj, long long in_width, int x_off, in
 // ------------------------------------------------------------------------------------------
 // the recurrence
 // ------------------------------------------------------------------------------------------
-// A block owns one head of one row and up to RC_PB of its P columns; thread (p, s) keeps the NREG
-// state elements n = s * NREG + r of column p in registers (RC_NS = 8 threads share a column:
-// their sums for y meet by shuffles).  Tokens come in chunks of RC_TC through shared memory.
+// A block owns one head of one row and up to RC_PB of its P columns.  RC_NS = 8 threads share a
+// column p: thread (p, s) keeps NREG elements of the column's state in registers, and the eight
+// partial sums of y meet by shuffles.  Which elements: with VEC (N a multiple of 4) the float4
+// groups s, s + 8, s + 16, .. (n = 4 (s + 8 j) + e), else the single elements s, s + 8, ..
+// (n = s + 8 r): either way the eight threads of a column read consecutive words of B and C in
+// shared memory (no bank conflicts; the other columns' threads read the same words) and
+// consecutive words of the state in memory.  Tokens come in chunks of RC_TC through shared memory.
 #define RC_NS 8
-#define RC_PB 64
-#define RC_TC 16
+#define RC_PB 32
+#define RC_TC 32
 
 struct ScanArgs {
     const float* u;           // [tokens][channels] conv output: x | B | C
@@ -143,10 +204,10 @@ struct ScanArgs {
     int heads, P, N, groups;
 };
 
-template <int NREG>
+template <int NREG, bool VEC>
 __global__ void __launch_bounds__(RC_PB * RC_NS) ssm_scan_kernel(ScanArgs a) {
     pdl_launch_dependents();
-    extern __shared__ float rc_smem[];
+    extern __shared__ __align__(16) float rc_smem[];
     const int b = blockIdx.x, h = blockIdx.y, p0 = blockIdx.z * RC_PB;
     const int tid = threadIdx.x, s = tid & (RC_NS - 1), pl = tid >> 3;
     const int p = p0 + pl;
@@ -165,13 +226,22 @@ __global__ void __launch_bounds__(RC_PB * RC_NS) ssm_scan_kernel(ScanArgs a) {
     const int t0 = a.cu_seqlens[b], n_b = a.cu_seqlens[b + 1] - t0;
     const int slot = a.slots[b];
     const int inner = a.heads * P;
+    // element r of this thread's registers is state element n_of(r) of its column
+    auto n_of = [&](int r) { return VEC ? 4 * (s + RC_NS * (r >> 2)) + (r & 3) : s + RC_NS * r; };
     pdl_wait();
     float* st = a.state + (((size_t)slot * a.heads + h) * P + (p_ok ? p : p0)) * N;
     float S[NREG];
+    if (VEC) {
 #pragma unroll
-    for (int r = 0; r < NREG; ++r) {
-        const int n = s * NREG + r;
-        S[r] = (p_ok && n < N) ? st[n] : 0.0f;
+        for (int j = 0; j < NREG / 4; ++j) {
+            const int n = 4 * (s + RC_NS * j);
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (p_ok && n < N) v = *reinterpret_cast<const float4*>(st + n);
+            S[4 * j] = v.x; S[4 * j + 1] = v.y; S[4 * j + 2] = v.z; S[4 * j + 3] = v.w;
+        }
+    } else {
+#pragma unroll
+        for (int r = 0; r < NREG; ++r) S[r] = (p_ok && n_of(r) < N) ? st[n_of(r)] : 0.0f;
     }
     for (int c0 = 0; c0 < n_b; c0 += RC_TC) {
         const int nc = min(RC_TC, n_b - c0);
@@ -195,14 +265,34 @@ __global__ void __launch_bounds__(RC_PB * RC_NS) ssm_scan_kernel(ScanArgs a) {
         for (int tt = 0; tt < nc; ++tt) {
             const float xv = p_ok ? xs[tt * RC_PB + pl] : 0.0f;
             const float da = das[tt], dtx = dts[tt] * xv;
-            const float* Bt = Bs + tt * N + s * NREG;
-            const float* Ct = Cs + tt * N + s * NREG;
+            const float* Bt = Bs + tt * N;
+            const float* Ct = Cs + tt * N;
             float acc = 0.0f;
+            if (VEC) {
 #pragma unroll
-            for (int r = 0; r < NREG; ++r) {
-                if (s * NREG + r < N) {
-                    S[r] = fmaf(da, S[r], dtx * Bt[r]);
-                    acc = fmaf(S[r], Ct[r], acc);
+                for (int j = 0; j < NREG / 4; ++j) {
+                    const int n = 4 * (s + RC_NS * j);
+                    if (n < N) {
+                        const float4 bv = *reinterpret_cast<const float4*>(Bt + n);
+                        const float4 cv = *reinterpret_cast<const float4*>(Ct + n);
+                        S[4 * j] = fmaf(da, S[4 * j], dtx * bv.x);
+                        S[4 * j + 1] = fmaf(da, S[4 * j + 1], dtx * bv.y);
+                        S[4 * j + 2] = fmaf(da, S[4 * j + 2], dtx * bv.z);
+                        S[4 * j + 3] = fmaf(da, S[4 * j + 3], dtx * bv.w);
+                        acc = fmaf(S[4 * j], cv.x, acc);
+                        acc = fmaf(S[4 * j + 1], cv.y, acc);
+                        acc = fmaf(S[4 * j + 2], cv.z, acc);
+                        acc = fmaf(S[4 * j + 3], cv.w, acc);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int r = 0; r < NREG; ++r) {
+                    const int n = s + RC_NS * r;
+                    if (n < N) {
+                        S[r] = fmaf(da, S[r], dtx * Bt[n]);
+                        acc = fmaf(S[r], Ct[n], acc);
+                    }
                 }
             }
             acc += __shfl_xor_sync(0xffffffffu, acc, 1);
@@ -213,10 +303,18 @@ __global__ void __launch_bounds__(RC_PB * RC_NS) ssm_scan_kernel(ScanArgs a) {
         }
     }
     if (p_ok) {
+        if (VEC) {
 #pragma unroll
-        for (int r = 0; r < NREG; ++r) {
-            const int n = s * NREG + r;
-            if (n < N) st[n] = S[r];
+            for (int j = 0; j < NREG / 4; ++j) {
+                const int n = 4 * (s + RC_NS * j);
+                if (n < N)
+                    *reinterpret_cast<float4*>(st + n) =
+                        make_float4(S[4 * j], S[4 * j + 1], S[4 * j + 2], S[4 * j + 3]);
+            }
+        } else {
+#pragma unroll
+            for (int r = 0; r < NREG; ++r)
+                if (n_of(r) < N) st[n_of(r)] = S[r];
         }
     }
 }
@@ -237,18 +335,27 @@ extern "C" int mf_ssm_scan(const float* u, const float* proj, long long in_width
     const int pb = P < RC_PB ? P : RC_PB;
     dim3 grid(n_rows, heads, (P + RC_PB - 1) / RC_PB), block(((pb * RC_NS + 31) / 32) * 32);
     const size_t smem = (size_t)(RC_TC * (RC_PB + 2 * N + 2)) * sizeof(float);
-    const int nreg = (N + RC_NS - 1) / RC_NS;
-#define MF_SCAN(NR) \
+    // float4 groups need rows of B, C and the state on 16-byte boundaries
+    const bool vec = N % 4 == 0 && ((uintptr_t)state & 15) == 0;
+    const int nreg = vec ? 4 * ((N / 4 + RC_NS - 1) / RC_NS) : (N + RC_NS - 1) / RC_NS;
+#define MF_SCAN(NR, V) \
     do { \
         if (smem > 48 * 1024) \
-            cudaFuncSetAttribute(ssm_scan_kernel<NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        mf_launch(ssm_scan_kernel<NR>, grid, block, smem, stream, a); \
+            cudaFuncSetAttribute(ssm_scan_kernel<NR, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        mf_launch(ssm_scan_kernel<NR, V>, grid, block, smem, stream, a); \
     } while (0)
-    if (nreg <= 2) MF_SCAN(2);
-    else if (nreg <= 4) MF_SCAN(4);
-    else if (nreg <= 8) MF_SCAN(8);
-    else if (nreg <= 16) MF_SCAN(16);
-    else MF_SCAN(32);
+    if (vec) {
+        if (nreg <= 4) MF_SCAN(4, true);
+        else if (nreg <= 8) MF_SCAN(8, true);
+        else if (nreg <= 16) MF_SCAN(16, true);
+        else MF_SCAN(32, true);
+    } else {
+        if (nreg <= 2) MF_SCAN(2, false);
+        else if (nreg <= 4) MF_SCAN(4, false);
+        else if (nreg <= 8) MF_SCAN(8, false);
+        else if (nreg <= 16) MF_SCAN(16, false);
+        else MF_SCAN(32, false);
+    }
 #undef MF_SCAN
     return MF_LAUNCH_CHECK();
 }
@@ -279,19 +386,104 @@ gated_group_norm_kernel(const float* __restrict__ y, const float* __restrict__ p
         o[i] = from_f32<TO>(yr[i] * rc_silu(zr[i]) * f * w[grp * gs + i]);
 }
 
+template <typename T> struct RcStore4;
+template <> struct RcStore4<float> {
+    static __device__ __forceinline__ void store(float* p, float a, float b, float c, float d) {
+        *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+    }
+};
+template <> struct RcStore4<__nv_bfloat16> {
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float a, float b, float c, float d) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+        uint2 v;
+        v.x = *reinterpret_cast<unsigned*>(&lo);
+        v.y = *reinterpret_cast<unsigned*>(&hi);
+        *reinterpret_cast<uint2*>(p) = v;
+    }
+};
+
+// the same with float4 accesses, one pass over memory (a thread keeps up to MAXV float4 of the
+// gated row in registers, all of its loads in flight together), for parts that are multiples of
+// 4 up to 4 * MAXV * blockDim
+#define GN_MAXV 4
+template <typename TO>
+__global__ void __launch_bounds__(1024)
+gated_group_norm_vec_kernel(const float* __restrict__ y, const float* __restrict__ proj,
+                            long long in_width, int z_off, const float* __restrict__ w,
+                            TO* __restrict__ out, int inner, int groups, float eps) {
+    pdl_launch_dependents();
+    __shared__ float scratch[33];
+    const int t = blockIdx.x, grp = blockIdx.y;
+    const int gs = inner / groups, nv = gs >> 2;
+    const float4* wr = reinterpret_cast<const float4*>(w + grp * gs);
+    float4 g[GN_MAXV];
+#pragma unroll
+    for (int j = 0; j < GN_MAXV; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < nv) g[j] = wr[i];
+    }
+    pdl_wait();
+    const float4* yr = reinterpret_cast<const float4*>(y + (size_t)t * inner + grp * gs);
+    const float4* zr = reinterpret_cast<const float4*>(proj + (size_t)t * in_width + z_off + grp * gs);
+    float4 v[GN_MAXV], z[GN_MAXV];
+#pragma unroll
+    for (int j = 0; j < GN_MAXV; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < nv) { v[j] = yr[i]; z[j] = zr[i]; }
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < GN_MAXV; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < nv) {
+            v[j].x *= rc_silu(z[j].x); v[j].y *= rc_silu(z[j].y);
+            v[j].z *= rc_silu(z[j].z); v[j].w *= rc_silu(z[j].w);
+            ss = fmaf(v[j].x, v[j].x, ss); ss = fmaf(v[j].y, v[j].y, ss);
+            ss = fmaf(v[j].z, v[j].z, ss); ss = fmaf(v[j].w, v[j].w, ss);
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float f = 1.0f / sqrtf(ss / (float)gs + eps);
+    TO* o = out + (size_t)t * inner + grp * gs;
+#pragma unroll
+    for (int j = 0; j < GN_MAXV; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < nv)
+            RcStore4<TO>::store(o + 4 * i, v[j].x * f * g[j].x, v[j].y * f * g[j].y, v[j].z * f * g[j].z,
+                                v[j].w * f * g[j].w);
+    }
+}
+
 extern "C" int mf_gated_group_norm(const float* y, const float* proj, long long in_width, int z_off,
                                    const float* w, void* out, int out_dtype, int n_tokens,
                                    int inner, int groups, float eps, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (groups < 1 || inner % groups != 0) return MF_ERR_ARGUMENT;
+    if (out_dtype != MF_DTYPE_F32 && out_dtype != MF_DTYPE_BF16) return MF_ERR_UNSUPPORTED;
     dim3 grid(n_tokens, groups);
+    const int gs = inner / groups;
+    // float4 accesses want every part of every row on a 16-byte boundary
+    const bool vec = gs % 4 == 0 && in_width % 4 == 0 && z_off % 4 == 0 && gs / 4 <= GN_MAXV * 1024 &&
+                     (((uintptr_t)y | (uintptr_t)proj | (uintptr_t)w | (uintptr_t)out) & 15) == 0;
+    if (vec) {
+        int threads = ((gs / 4 + GN_MAXV - 1) / GN_MAXV + 31) / 32 * 32;
+        // few tokens: as many threads as float4, so that a row is one round trip
+        if (n_tokens * groups < 2 * mf_sm_count()) threads = (gs / 4 + 31) / 32 * 32;
+        if (threads > 1024) threads = 1024;
+        if (threads < 32) threads = 32;
+        if (out_dtype == MF_DTYPE_F32)
+            mf_launch(gated_group_norm_vec_kernel<float>, grid, dim3(threads), 0, stream, y, proj, in_width,
+                      z_off, w, (float*)out, inner, groups, eps);
+        else
+            mf_launch(gated_group_norm_vec_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, y, proj,
+                      in_width, z_off, w, (__nv_bfloat16*)out, inner, groups, eps);
+        return MF_LAUNCH_CHECK();
+    }
     if (out_dtype == MF_DTYPE_F32)
         mf_launch(gated_group_norm_kernel<float>, grid, dim3(256), 0, stream, y, proj, in_width, z_off,
                   w, (float*)out, inner, groups, eps);
-    else if (out_dtype == MF_DTYPE_BF16)
+    else
         mf_launch(gated_group_norm_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, y, proj, in_width,
                   z_off, w, (__nv_bfloat16*)out, inner, groups, eps);
-    else
-        return MF_ERR_UNSUPPORTED;
     return MF_LAUNCH_CHECK();
 }

@@ -191,7 +191,7 @@ def _sig_attention_prefill_tc(lib: ctypes.CDLL) -> None:
 
 
     lib.mf_sink_attention_tc.argtypes = ([c_void_p] * 6 + [c_int, c_int] + [c_void_p] * 3 + [c_int] * 9 +
-                                         [c_float, c_longlong, c_void_p, c_void_p])
+                                         [c_float, c_longlong, c_void_p, c_float, c_void_p, c_void_p])
 
 
 def _sig_recurrent(lib: ctypes.CDLL) -> None:
@@ -871,8 +871,8 @@ def qk_prepare(proj: torch.Tensor, positions: torch.Tensor, token_row: torch.Ten
             raise KernelError("qk_prepare: q, k, v and the cache must share one dtype")
     if q_out.numel() != n * n_heads * q_width:
         raise KernelError("qk_prepare: q has the wrong size")
-    if k_cache is not None and (k_cache.shape[-1] != k_width or v_cache.shape[-1] != v_width
-                                or k_cache.shape[1] != n_kv):
+    if k_cache is not None and (k_cache.shape[-1] != k_width or k_cache.shape[1] != n_kv or
+                                (v_cache is not None and v_cache.shape[-1] != v_width)):
         raise KernelError("qk_prepare: the cache has other key or value widths")
     need = max(q_off + n_heads * q_width, k_off + n_kv * k_width,
                0 if v_from_k else v_off + n_kv * v_width)
@@ -1051,7 +1051,8 @@ def sink_attention_tc(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seql
                       table_stride: int, ring: int, out: torch.Tensor, r1: Optional[torch.Tensor],
                       r2: Optional[torch.Tensor], n_rows: int, max_row_tokens: int, n_heads: int,
                       n_kv: int, head_dim: int, window: int, chunk: int, sink: bool, scale: float,
-                      status: torch.Tensor) -> None:
+                      status: torch.Tensor, sink_logit: Optional[torch.Tensor] = None,
+                      softcap: float = 0.0) -> None:
     """``sink_attention_mma``'s job on the 5th-generation tensor cores (tcgen05, tensor memory):
     the step's packed queries over the step's own keys (``page_table`` None) or over the cache."""
     n = q.shape[0]
@@ -1065,7 +1066,8 @@ def sink_attention_tc(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seql
         _i32(seq_end, "seq_end"), _i32(page_table, "page_table"), int(table_stride), int(ring),
         _ptr(out, "out"), _f32(r1, "r1"), _f32(r2, "r2"), n, int(n_rows), int(max_row_tokens),
         n_heads, n_kv, head_dim, int(window), int(chunk), 1 if sink else 0, float(scale), int(pages),
-        _i32(status, "status"), _stream()), "sink_attention_tc")
+        _f32(sink_logit, "sink_logit"), float(softcap), _i32(status, "status"), _stream()),
+        "sink_attention_tc")
 
 
 _SINK_PLANS: dict = {}

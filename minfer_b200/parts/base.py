@@ -36,6 +36,9 @@ class CacheRequest:
     head_dim: int
     window: int = 0
     value_dim: int = 0       # width of a value vector if it differs from the keys' (0: head_dim)
+    # the values ARE the keys (one latent vector per position serves as both): the cache keeps one
+    # tensor and hands it out as K and as V
+    shared_values: bool = False
 
 
 @dataclass(frozen=True)

@@ -12,10 +12,13 @@ Computed in the absorbed form, which never expands the latent into per-head keys
     q'_h = [Wuk_h^T q_p | q_r]   (kv_rank + rot_dim wide),   key_j = [c_j | k_r_j] shared by all
     heads,   value_j = c_j,   o_h = Wuv_h (sum_j w_ij c_j)
 since q_p . (Wuk_h c) = (Wuk_h^T q_p) . c.  The attention is therefore one over a single
-key/value head of width kv_rank + rot_dim with values of width kv_rank
-(``parts.sink_attention.scored_attention``), between two per-head products
-(``kernels.api.head_linear``; the second applies the gate).  The cache entry holds [c | k_r] as
-its key and c as its value; with a window it is a ring.
+key/value head of width kv_rank + rot_dim (``parts.sink_attention.scored_attention``), between
+two per-head products (``kernels.api.head_linear``; the second applies the gate).  The value IS
+the key: the attention kernels get the same tensor [c | k_r] for both, and the second product
+reads the first kv_rank columns of the weighted sum (the rot_dim columns behind them are
+computed and ignored: a third more work in P V, for keys and values of one size, which is what
+the tensor-memory kernel takes, and for a cache that holds each position's vector once).  With a
+window the cache entry is a ring.
 
 One packed product gives q | c' | k_r | gate in float32.  Tensor names behind ``prefix +
 tensor_prefix``: ``q``, ``dkv``, ``dkv.norm``, ``uk``, ``uv``, ``sink``, ``g``, ``o``.
@@ -40,6 +43,9 @@ class LatentAttention(Mixer):
     def libraries(self, dtype: torch.dtype) -> List[str]:
         libs = ["ops", "mixer_prep", "attention_sink"]
         libs.append("gemm_tc" if dtype == torch.bfloat16 else "gemm_simt")
+        kw = self.kv_rank + self.rot_dim
+        if K.sink_attention_tc_supported(dtype, kw, kw):
+            libs.append("attention_prefill_tc")
         return libs
 
     def __init__(self, hidden_size: int, n_heads: int, head_dim: int, rot_dim: int, value_dim: int,
@@ -127,12 +133,13 @@ class LatentAttention(Mixer):
 
     # ---- what it keeps per sequence -----------------------------------------------------
     def cache_request(self) -> Optional[CacheRequest]:
-        return CacheRequest(1, self.kv_rank + self.rot_dim, self.window, self.kv_rank)
+        return CacheRequest(1, self.kv_rank + self.rot_dim, self.window, shared_values=True)
 
     def scores(self) -> ScoreSpec:
-        return ScoreSpec(n_heads=self.n_heads, n_kv_heads=1, head_dim=self.kv_rank + self.rot_dim,
-                         value_dim=self.kv_rank, scale=self.scale, window=self.window,
-                         sink=self.sink, sink_logit=self.sink_logit)
+        kw = self.kv_rank + self.rot_dim
+        return ScoreSpec(n_heads=self.n_heads, n_kv_heads=1, head_dim=kw, value_dim=kw,
+                         scale=self.scale, window=self.window, sink=self.sink,
+                         sink_logit=self.sink_logit)
 
     # ---- the step -----------------------------------------------------------------------
     def forward_add(self, x: torch.Tensor, ctx: StepContext, binding: CallBinding,
@@ -155,18 +162,17 @@ class LatentAttention(Mixer):
         q = torch.empty((n, nh * (hd + rd)), dtype=act, device=dev)
         write = binding.writes_cache
         own_kv = ctx.from_start
-        k_step = v_step = None
+        k_step = None
         if own_kv and write:
             k_step = torch.empty((n, 1, kw), dtype=act, device=dev)
-            v_step = torch.empty((n, 1, rank), dtype=act, device=dev)
             if binding.has_readers:
-                ctx.extras[("step_kv", binding.entry)] = (k_step, v_step)
+                ctx.extras[("step_kv", binding.entry)] = (k_step, k_step)
         elif own_kv:
-            k_step, v_step = ctx.extras[("step_kv", binding.entry)]
-        # q: rotated part turned; key: latent normed, rotated part turned; value: the latent
+            k_step, _ = ctx.extras[("step_kv", binding.entry)]
+        # q: rotated part turned; key: latent normed, rotated part turned; the value is the key
         K.qk_prepare(proj, ctx.positions, ctx.token_row, ctx.seq_end, q,
-                     k_step if write else None, v_step if write else None,
-                     cache.k if write else None, cache.v if write else None,
+                     k_step if write else None, None,
+                     cache.k if write else None, None,
                      cache.page_table if write else None, cache.table_stride, cache.ring,
                      q_off=0, n_heads=nh, q_width=hd + rd, k_off=nq, n_kv=1, k_width=kw,
                      v_off=0, v_width=rank, v_from_k=True, q_norm=None, k_norm=self.c_norm,
@@ -175,10 +181,10 @@ class LatentAttention(Mixer):
         # q'_h = [Wuk_h^T q_p | q_r]
         q_abs = torch.empty((n, nh * kw), dtype=act, device=dev)
         K.head_linear(q, self.uk_t, q_abs, x_head=hd + rd, x_off=0, y_head=kw, tail=rd, x_tail_off=hd)
-        o_lat = torch.empty((n, nh * rank), dtype=act, device=dev)
-        scored_attention(self.scores(), q_abs.view(n, nh, kw), k_step, v_step, cache, ctx, o_lat)
-        # o_h = Wuv_h (weighted latent), times the gate
+        o_lat = torch.empty((n, nh * kw), dtype=act, device=dev)
+        scored_attention(self.scores(), q_abs.view(n, nh, kw), k_step, k_step, cache, ctx, o_lat)
+        # o_h = Wuv_h (the first kv_rank columns of the weighted sum), times the gate
         o = torch.empty((n, nh * vd), dtype=act, device=dev)
-        K.head_linear(o_lat, self.uv, o, x_head=rank, x_off=0, y_head=vd,
+        K.head_linear(o_lat, self.uv, o, x_head=kw, x_off=0, y_head=vd,
                       gate=proj if self.gate else None, gate_off=nq + kw)
         project_out(self.out, o, ctx, residual)

@@ -34,6 +34,8 @@ class QkNormAttention(Mixer):
     def libraries(self, dtype: torch.dtype) -> List[str]:
         libs = ["ops", "mixer_prep", "attention_sink"]
         libs.append("gemm_tc" if dtype == torch.bfloat16 else "gemm_simt")
+        if K.sink_attention_tc_supported(dtype, self.head_dim, self.value_dim):
+            libs.append("attention_prefill_tc")
         return libs
 
     def __init__(self, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int,

@@ -83,14 +83,13 @@ def scored_attention(spec: ScoreSpec, q: torch.Tensor, k_step: Optional[torch.Te
     r1, r2 = spec.r1, spec.r2
     cap, sl = spec.softcap, spec.sink_logit
     tensor_cores = K.sink_attention_mma_supported(act, hd, vd) and not FORCE_GENERIC
-    # prompts: the tcgen05 kernel where keys and values have one size it takes (it knows neither
-    # a soft cap nor a learned score of the sink), else mma.sync
-    tcgen05 = (tensor_cores and PROMPT_KERNEL != "mma" and cap == 0.0 and sl is None
+    # prompts: the tcgen05 kernel where keys and values have one size it takes, else mma.sync
+    tcgen05 = (tensor_cores and PROMPT_KERNEL != "mma" and spec.scale > 0.0
                and K.sink_attention_tc_supported(act, hd, vd))
     if own_kv and tcgen05:
         K.sink_attention_tc(q, k_step, v_step, ctx.cu_seqlens, None, None, 0, 0, o, r1, r2,
                             ctx.n_rows, ctx.max_row_tokens, nh, nk, hd, spec.window, spec.chunk,
-                            spec.sink, spec.scale, ctx.status)
+                            spec.sink, spec.scale, ctx.status, sink_logit=sl, softcap=cap)
         return
     if own_kv and tensor_cores:
         K.sink_attention_mma(q, k_step, v_step, ctx.cu_seqlens, None, None, 0, 0, o, r1, r2,
@@ -112,7 +111,7 @@ def scored_attention(spec: ScoreSpec, q: torch.Tensor, k_step: Optional[torch.Te
         K.sink_attention_tc(q, cache.k, cache.v, ctx.cu_seqlens, ctx.seq_end, cache.page_table,
                             cache.table_stride, cache.ring, o, r1, r2, ctx.n_rows,
                             ctx.max_row_tokens, nh, nk, hd, spec.window, spec.chunk, spec.sink,
-                            spec.scale, ctx.status)
+                            spec.scale, ctx.status, sink_logit=sl, softcap=cap)
         return
     if tensor_cores and not ctx.single_token and ctx.n_tokens >= PAGED_PROMPT_MIN_TOKENS:
         # rows of several tokens: query tiles of the step's rows over the cache's pages

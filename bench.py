@@ -621,12 +621,12 @@ def budanex_kernels(torch, K, pk, width, heads, kv, dim, ssm_heads, lat_heads, w
         qa = torch.empty(n, lat_heads * 128, dtype=bf, device=dev)
         uk = (torch.randn(lat_heads, 96, 64, device=dev) * 0.1).to(bf)
         uv = (torch.randn(lat_heads, 64, 96, device=dev) * 0.1).to(bf)
-        ol = torch.randn(n, lat_heads * 96, device=dev).to(bf)
+        ol = torch.randn(n, lat_heads * 128, device=dev).to(bf)
         o = torch.empty(n, lat_heads * 64, dtype=bf, device=dev)
         timed(f"head_linear_uk_{label}", lambda: K.head_linear(q, uk, qa, x_head=96, x_off=0, y_head=128,
                                                                tail=32, x_tail_off=64),
               n * lat_heads * (96 + 128) * 2 + uk.numel() * 2)
-        timed(f"head_linear_uv_gate_{label}", lambda: K.head_linear(ol, uv, o, x_head=96, x_off=0, y_head=64,
+        timed(f"head_linear_uv_gate_{label}", lambda: K.head_linear(ol, uv, o, x_head=128, x_off=0, y_head=64,
                                                                     gate=lproj, gate_off=lat_heads * 96 + 128),
               n * lat_heads * (96 * 2 + 64 * 2 + 64 * 4) + uv.numel() * 2)
     # attention kernels with and without the design's modifiers, over packed keys (a prompt) ...
@@ -634,7 +634,7 @@ def budanex_kernels(torch, K, pk, width, heads, kv, dim, ssm_heads, lat_heads, w
     cu1 = torch.tensor([0, tokens], dtype=torch.int32, device=dev)
     peak = pk["bf16_tflops"] * 1e12
     for name, nh, nk, hd, vd, win, cap, with_sink in (("attention", heads, kv, dim, dim, 0, 50.0, False),
-                                                       ("latent", lat_heads, 1, 128, 96, window, 0.0, True)):
+                                                       ("latent", lat_heads, 1, 128, 128, window, 0.0, True)):
         qq = (torch.randn(tokens, nh, hd, device=dev) * 0.5).to(bf)
         kk = (torch.randn(tokens, nk, hd, device=dev) * 0.5).to(bf)
         vv = torch.randn(tokens, nk, vd, device=dev).to(bf)
@@ -649,6 +649,12 @@ def budanex_kernels(torch, K, pk, width, heads, kv, dim, ssm_heads, lat_heads, w
             out[f"{name}_prompt_mma{tag}"] = {"us": round(ms * 1e3, 1),
                                               "frac_of_product_peak": round(fl / (ms * 1e-3) / peak, 4)}
         if hd == vd:
+            for tag, c, sk in (("", cap, sink), ("_plain_scores", 0.0, None)):
+                ms = _median_ms(torch, lambda: K.sink_attention_tc(
+                    qq, kk, vv, cu1, None, None, 0, 0, oo, None, None, 1, tokens, nh, nk, hd, win, 0,
+                    with_sink, hd ** -0.5, status, sink_logit=sk, softcap=c), 20, flush)
+                out[f"{name}_prompt_tcgen05{tag}"] = {"us": round(ms * 1e3, 1),
+                                                      "frac_of_product_peak": round(fl / (ms * 1e-3) / peak, 4)}
             ms = _median_ms(torch, lambda: K.attention_prefill_tc(qq, kk, vv, cu1, oo, 1, tokens, nh, nk, hd,
                                                                   win, hd ** -0.5, status), 20, flush)
             out[f"{name}_prompt_qwen2_tcgen05"] = {"us": round(ms * 1e3, 1),

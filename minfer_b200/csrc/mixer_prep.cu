@@ -1,7 +1,8 @@
 // What attention mixers do between their input projection and the attention itself, for layouts
 // the fused rotary kernel does not take, and the small per-head products of latent attention.
 //
-//   qk_prepare     One block per token.  From the projection's float32 row it takes a query
+//   qk_prepare     One block per token (several when tokens are few: each forms the norms' sums
+//                  itself and takes a share of the elements).  From the projection's float32 row it takes a query
 //                  segment (n_heads heads of qw) and a key segment (n_kv heads of kw), optionally
 //                  RMS-norms the first q_norm_n / k_norm_n elements of each segment AS A WHOLE
 //                  (all heads at once: x / sqrt(mean(x^2) + eps) * weight), rotates `rot_dims`
@@ -95,7 +96,7 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(PrepArgs a) {
         }
         if (keep) {
             page = a.page_table[(size_t)b * a.table_stride + (p_eff >> 6)];
-            if (page < 0 && threadIdx.x == 0) atomicOr(a.status, MF_STATUS_BAD_POSITION);
+            if (page < 0 && threadIdx.x == 0 && blockIdx.y == 0) atomicOr(a.status, MF_STATUS_BAD_POSITION);
         }
     }
     pdl_wait();
@@ -118,13 +119,14 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(PrepArgs a) {
     __syncthreads();                                  // the cosines and sines are written
     T* q_out = (T*)a.q_out + (size_t)t * a.n_heads * a.qw;
     const int nq = a.n_heads * a.qw;
-    for (int e = threadIdx.x; e < nq; e += blockDim.x) {
+    const int first = blockIdx.y * blockDim.x + threadIdx.x, stride = gridDim.y * blockDim.x;
+    for (int e = first; e < nq; e += stride) {
         const int d = e % a.qw;
         q_out[e] = from_f32<T>(prep_value(qs, a.q_norm_w, a.q_norm_n, q_rinv, a.qw, d, e, a.q_rot_off, a, pr_cs));
     }
     const int in_page = pos & (MF_PAGE - 1);
     const int nk = a.n_kv * a.kw;
-    for (int e = threadIdx.x; e < nk; e += blockDim.x) {
+    for (int e = first; e < nk; e += stride) {
         const int hk = e / a.kw, d = e - hk * a.kw;
         const T y = from_f32<T>(prep_value(ks, a.k_norm_w, a.k_norm_n, k_rinv, a.kw, d, e, a.k_rot_off, a, pr_cs));
         if (a.k_out) ((T*)a.k_out)[(size_t)t * nk + e] = y;
@@ -139,7 +141,7 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(PrepArgs a) {
     if (!a.v_from_k) {
         const float* vs = row + a.v_off;
         const int nv = a.n_kv * a.vw;
-        for (int e = threadIdx.x; e < nv; e += blockDim.x) {
+        for (int e = first; e < nv; e += stride) {
             const int hk = e / a.vw, d = e - hk * a.vw;
             const T y = from_f32<T>(vs[e]);
             if (a.v_out) ((T*)a.v_out)[(size_t)t * nv + e] = y;
@@ -161,10 +163,19 @@ extern "C" int mf_qk_prepare(const PrepArgs* args, int n_tokens, int dtype, cuda
     if (a.v_from_k && a.vw > a.kw) return MF_ERR_ARGUMENT;
     // a rotated pair must lie wholly inside or wholly outside the normed stretch of its segment
     const size_t smem = (size_t)(a.rot_dims > 0 ? a.rot_dims : 2) * sizeof(float);
+    // few tokens: a token's elements are spread over up to 8 blocks
+    int by = 1;
+    if (n_tokens < 2 * mf_sm_count()) {
+        const int widest = a.n_heads * a.qw > a.n_kv * a.kw ? a.n_heads * a.qw : a.n_kv * a.kw;
+        by = (widest + 511) / 512;
+        if (by > 8) by = 8;
+        if (by < 1) by = 1;
+    }
+    dim3 grid(n_tokens, by);
     if (dtype == MF_DTYPE_F32)
-        mf_launch(qk_prepare_kernel<float>, dim3(n_tokens), dim3(256), smem, stream, a);
+        mf_launch(qk_prepare_kernel<float>, grid, dim3(256), smem, stream, a);
     else if (dtype == MF_DTYPE_BF16)
-        mf_launch(qk_prepare_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(256), smem, stream, a);
+        mf_launch(qk_prepare_kernel<__nv_bfloat16>, grid, dim3(256), smem, stream, a);
     else
         return MF_ERR_UNSUPPORTED;
     return MF_LAUNCH_CHECK();
@@ -173,8 +184,8 @@ extern "C" int mf_qk_prepare(const PrepArgs* args, int n_tokens, int dtype, cuda
 // ------------------------------------------------------------------------------------------
 // per-head products
 // ------------------------------------------------------------------------------------------
-#define HL_TT 32          // tokens per block
-#define HL_TJ 32          // outputs per block
+#define HL_TT 64          // tokens per block
+#define HL_TJ 64          // outputs per block
 #define HL_TD 32          // reduction chunk
 
 struct HeadLinearArgs {
@@ -188,6 +199,7 @@ struct HeadLinearArgs {
     int tail, x_tail_off;     // copy x[t][h][x_tail_off .. + tail) to y[t][h][J ..)
 };
 
+// a thread owns 4 x 4 results: tokens ty + 16 i, outputs tx + 16 j
 template <typename T>
 __global__ void __launch_bounds__(256) head_linear_kernel(HeadLinearArgs a) {
     pdl_prologue();
@@ -196,10 +208,14 @@ __global__ void __launch_bounds__(256) head_linear_kernel(HeadLinearArgs a) {
     const int h = blockIdx.z;
     const int t0 = blockIdx.x * HL_TT, j0 = blockIdx.y * HL_TJ;
     const int tid = threadIdx.x;
-    const int tj = tid & 31, tt = tid >> 5;          // outputs j0 + tj, tokens t0 + tt + 8 i
+    const int tx = tid & 15, ty = tid >> 4;
     const T* x = (const T*)a.x;
     const T* w = (const T*)a.w + (size_t)h * a.J * a.D;
-    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
     for (int d0 = 0; d0 < a.D; d0 += HL_TD) {
         for (int i = tid; i < HL_TT * HL_TD; i += 256) {
             const int r = i >> 5, d = i & 31;
@@ -212,24 +228,31 @@ __global__ void __launch_bounds__(256) head_linear_kernel(HeadLinearArgs a) {
         __syncthreads();
 #pragma unroll
         for (int d = 0; d < HL_TD; ++d) {
-            const float wv = ws[tj][d];
+            float xv[4], wv[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) acc[i] = fmaf(xs[tt + 8 * i][d], wv, acc[i]);
+            for (int i = 0; i < 4; ++i) { xv[i] = xs[ty + 16 * i][d]; wv[i] = ws[tx + 16 * i][d]; }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(xv[i], wv[j], acc[i][j]);
         }
         __syncthreads();
     }
-    const int j = j0 + tj;
     T* y = (T*)a.y;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const int tok = t0 + tt + 8 * i;
-        if (tok < a.n_tokens && j < a.J) {
-            float v = acc[i];
-            if (a.gate) {
-                const float gv = a.gate[(size_t)tok * a.gate_row + a.gate_off + (size_t)h * a.J + j];
-                v *= 1.0f / (1.0f + expf(-gv));
+        const int tok = t0 + ty + 16 * i;
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+            const int j = j0 + tx + 16 * jj;
+            if (tok < a.n_tokens && j < a.J) {
+                float v = acc[i][jj];
+                if (a.gate) {
+                    const float gv = a.gate[(size_t)tok * a.gate_row + a.gate_off + (size_t)h * a.J + j];
+                    v *= 1.0f / (1.0f + expf(-gv));
+                }
+                y[(size_t)tok * a.y_row + (size_t)h * a.y_head + j] = from_f32<T>(v);
             }
-            y[(size_t)tok * a.y_row + (size_t)h * a.y_head + j] = from_f32<T>(v);
         }
     }
     if (a.tail > 0 && blockIdx.y == 0) {

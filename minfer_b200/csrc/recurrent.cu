@@ -178,13 +178,14 @@ extern "C" int mf_conv_silu(const float* proj, long long in_width, int x_off, in
 // ------------------------------------------------------------------------------------------
 // the recurrence
 // ------------------------------------------------------------------------------------------
-// A block owns one head of one row and up to RC_PB of its P columns.  RC_NS = 8 threads share a
+// A block owns one head of one row and up to RC_PB of its P columns.  NS = 8 or 16 threads share a
 // column p: thread (p, s) keeps NREG elements of the column's state in registers, and the eight
 // partial sums of y meet by shuffles.  Which elements: with VEC (N a multiple of 4) the float4
 // groups s, s + 8, s + 16, .. (n = 4 (s + 8 j) + e), else the single elements s, s + 8, ..
 // (n = s + 8 r): either way the eight threads of a column read consecutive words of B and C in
 // shared memory (no bank conflicts; the other columns' threads read the same words) and
-// consecutive words of the state in memory.  Tokens come in chunks of RC_TC through shared memory.
+// consecutive words of the state in memory.  Tokens come in chunks of RC_TC through two buffers in
+// shared memory filled by cp.async: the next chunk travels while this one is walked.
 #define RC_NS 8
 #define RC_PB 32
 #define RC_TC 32
@@ -204,21 +205,88 @@ struct ScanArgs {
     int heads, P, N, groups;
 };
 
-template <int NREG, bool VEC>
-__global__ void __launch_bounds__(RC_PB * RC_NS) ssm_scan_kernel(ScanArgs a) {
+__device__ __forceinline__ void rc_cp_async4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;"
+                 ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void rc_cp_async16(float* dst, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;"
+                 ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
+#define RC_TU 4
+
+// TU consecutive tokens of a chunk, from token `tt` on: S <- da S + dt x B, y = S . C + D x for
+// each in turn (S carries over), the TU sums reduced over a column's eight threads together.
+template <int NREG, bool VEC, int TU, int NS>
+__device__ __forceinline__ void rc_walk(float (&S)[NREG], const float* xs, const float* Bs, const float* Cs,
+                                        const float* dts, const float* das, int tt, int N, int s, int pl,
+                                        bool p_ok, float dsk, float* y_col, int inner) {
+    float xv[TU], da[TU], dtx[TU], acc[TU];
+#pragma unroll
+    for (int u = 0; u < TU; ++u) {
+        xv[u] = p_ok ? xs[(tt + u) * RC_PB + pl] : 0.0f;
+        da[u] = das[tt + u];
+        dtx[u] = dts[tt + u] * xv[u];
+        acc[u] = 0.0f;
+    }
+    if (VEC) {
+#pragma unroll
+        for (int j = 0; j < NREG / 4; ++j) {
+            const int n = 4 * (s + NS * j);
+            if (n < N) {
+#pragma unroll
+                for (int u = 0; u < TU; ++u) {
+                    const float4 bv = *reinterpret_cast<const float4*>(Bs + (tt + u) * N + n);
+                    const float4 cv = *reinterpret_cast<const float4*>(Cs + (tt + u) * N + n);
+                    S[4 * j] = fmaf(da[u], S[4 * j], dtx[u] * bv.x);
+                    S[4 * j + 1] = fmaf(da[u], S[4 * j + 1], dtx[u] * bv.y);
+                    S[4 * j + 2] = fmaf(da[u], S[4 * j + 2], dtx[u] * bv.z);
+                    S[4 * j + 3] = fmaf(da[u], S[4 * j + 3], dtx[u] * bv.w);
+                    acc[u] += fmaf(S[4 * j + 3], cv.w,
+                                   fmaf(S[4 * j + 2], cv.z, fmaf(S[4 * j + 1], cv.y, S[4 * j] * cv.x)));
+                }
+            }
+        }
+    } else {
+#pragma unroll
+        for (int r = 0; r < NREG; ++r) {
+            const int n = s + NS * r;
+            if (n < N) {
+#pragma unroll
+                for (int u = 0; u < TU; ++u) {
+                    S[r] = fmaf(da[u], S[r], dtx[u] * Bs[(tt + u) * N + n]);
+                    acc[u] = fmaf(S[r], Cs[(tt + u) * N + n], acc[u]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 1; o < NS; o <<= 1) {
+#pragma unroll
+        for (int u = 0; u < TU; ++u) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], o);
+    }
+    if (s == 0 && p_ok) {
+#pragma unroll
+        for (int u = 0; u < TU; ++u) y_col[(size_t)(tt + u) * inner] = fmaf(dsk, xv[u], acc[u]);
+    }
+}
+
+template <int NREG, bool VEC, int NS>
+__global__ void __launch_bounds__(RC_PB * NS) ssm_scan_kernel(ScanArgs a) {
     pdl_launch_dependents();
     extern __shared__ __align__(16) float rc_smem[];
     const int b = blockIdx.x, h = blockIdx.y, p0 = blockIdx.z * RC_PB;
-    const int tid = threadIdx.x, s = tid & (RC_NS - 1), pl = tid >> 3;
+    const int tid = threadIdx.x, s = tid & (NS - 1), pl = tid / NS;
     const int p = p0 + pl;
     const int n_p = min(RC_PB, a.P - p0);
     const bool p_ok = pl < n_p;
     const int N = a.N, P = a.P;
-    float* xs = rc_smem;                          // [TC][RC_PB]
-    float* Bs = xs + RC_TC * RC_PB;               // [TC][N]
-    float* Cs = Bs + RC_TC * N;                   // [TC][N]
-    float* dts = Cs + RC_TC * N;                  // [TC]
-    float* das = dts + RC_TC;                     // [TC]
+    // two buffers of a chunk's x, B and C (the next chunk travels while this one is walked),
+    // then the chunks' step sizes and decays
+    const int buf_floats = RC_TC * (RC_PB + 2 * N);
+    float* dts = rc_smem + 2 * buf_floats;        // [2][TC]
+    float* das = dts + 2 * RC_TC;                 // [2][TC]
     const int g = h / (a.heads / a.groups);
     const float bias = a.dt_bias[h];
     const float rate = expf(a.a_log[h]);
@@ -227,14 +295,59 @@ __global__ void __launch_bounds__(RC_PB * RC_NS) ssm_scan_kernel(ScanArgs a) {
     const int slot = a.slots[b];
     const int inner = a.heads * P;
     // element r of this thread's registers is state element n_of(r) of its column
-    auto n_of = [&](int r) { return VEC ? 4 * (s + RC_NS * (r >> 2)) + (r & 3) : s + RC_NS * r; };
+    auto n_of = [&](int r) { return VEC ? 4 * (s + NS * (r >> 2)) + (r & 3) : s + NS * r; };
+    // x may be copied 16 bytes at a time when its rows and this block's columns start on
+    // 16-byte boundaries
+    const bool x16 = VEC && (a.channels & 3) == 0 && ((h * P + p0) & 3) == 0 && (n_p & 3) == 0;
     pdl_wait();
+    auto fetch = [&](int c0, int buf) {
+        const int nc = min(RC_TC, n_b - c0);
+        float* xs = rc_smem + buf * buf_floats;
+        float* Bs = xs + RC_TC * RC_PB;
+        float* Cs = Bs + RC_TC * N;
+        const float* base = a.u + (size_t)(t0 + c0) * a.channels;
+        if (x16) {
+            const int q = n_p >> 2;
+            for (int i = tid; i < nc * q; i += blockDim.x) {
+                const int tt = i / q, pp = (i - tt * q) << 2;
+                rc_cp_async16(xs + tt * RC_PB + pp, base + (size_t)tt * a.channels + h * P + p0 + pp);
+            }
+        } else {
+            for (int i = tid; i < nc * n_p; i += blockDim.x) {
+                const int tt = i / n_p, pp = i - tt * n_p;
+                rc_cp_async4(xs + tt * RC_PB + pp, base + (size_t)tt * a.channels + h * P + p0 + pp);
+            }
+        }
+        if (VEC && (a.channels & 3) == 0 && ((inner + g * N) & 3) == 0) {
+            const int q = N >> 2;
+            for (int i = tid; i < nc * q; i += blockDim.x) {
+                const int tt = i / q, n = (i - tt * q) << 2;
+                const float* row = base + (size_t)tt * a.channels + inner + g * N + n;
+                rc_cp_async16(Bs + tt * N + n, row);
+                rc_cp_async16(Cs + tt * N + n, row + (size_t)a.groups * N);
+            }
+        } else {
+            for (int i = tid; i < nc * N; i += blockDim.x) {
+                const int tt = i / N, n = i - tt * N;
+                const float* row = base + (size_t)tt * a.channels + inner + g * N + n;
+                rc_cp_async4(Bs + tt * N + n, row);
+                rc_cp_async4(Cs + tt * N + n, row + (size_t)a.groups * N);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        if (tid < nc) {
+            const float dt = rc_softplus(a.proj[(size_t)(t0 + c0 + tid) * a.in_width + a.dt_off + h] + bias);
+            dts[buf * RC_TC + tid] = dt;
+            das[buf * RC_TC + tid] = expf(-rate * dt);
+        }
+    };
+    if (n_b > 0) fetch(0, 0);
     float* st = a.state + (((size_t)slot * a.heads + h) * P + (p_ok ? p : p0)) * N;
     float S[NREG];
     if (VEC) {
 #pragma unroll
         for (int j = 0; j < NREG / 4; ++j) {
-            const int n = 4 * (s + RC_NS * j);
+            const int n = 4 * (s + NS * j);
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
             if (p_ok && n < N) v = *reinterpret_cast<const float4*>(st + n);
             S[4 * j] = v.x; S[4 * j + 1] = v.y; S[4 * j + 2] = v.z; S[4 * j + 3] = v.w;
@@ -243,70 +356,36 @@ __global__ void __launch_bounds__(RC_PB * RC_NS) ssm_scan_kernel(ScanArgs a) {
 #pragma unroll
         for (int r = 0; r < NREG; ++r) S[r] = (p_ok && n_of(r) < N) ? st[n_of(r)] : 0.0f;
     }
-    for (int c0 = 0; c0 < n_b; c0 += RC_TC) {
+    int buf = 0;
+    for (int c0 = 0; c0 < n_b; c0 += RC_TC, buf ^= 1) {
         const int nc = min(RC_TC, n_b - c0);
-        __syncthreads();
-        for (int i = tid; i < nc * n_p; i += blockDim.x) {
-            const int tt = i / n_p, pp = i - tt * n_p;
-            xs[tt * RC_PB + pp] = a.u[(size_t)(t0 + c0 + tt) * a.channels + h * P + p0 + pp];
-        }
-        for (int i = tid; i < nc * N; i += blockDim.x) {
-            const int tt = i / N, n = i - tt * N;
-            const float* row = a.u + (size_t)(t0 + c0 + tt) * a.channels + inner + g * N + n;
-            Bs[tt * N + n] = row[0];
-            Cs[tt * N + n] = row[(size_t)a.groups * N];
-        }
-        if (tid < nc) {
-            const float dt = rc_softplus(a.proj[(size_t)(t0 + c0 + tid) * a.in_width + a.dt_off + h] + bias);
-            dts[tid] = dt;
-            das[tid] = expf(-rate * dt);
+        if (c0 + RC_TC < n_b) {
+            fetch(c0 + RC_TC, buf ^ 1);           // (that buffer's walk ended at the barrier below)
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncthreads();
-        for (int tt = 0; tt < nc; ++tt) {
-            const float xv = p_ok ? xs[tt * RC_PB + pl] : 0.0f;
-            const float da = das[tt], dtx = dts[tt] * xv;
-            const float* Bt = Bs + tt * N;
-            const float* Ct = Cs + tt * N;
-            float acc = 0.0f;
-            if (VEC) {
-#pragma unroll
-                for (int j = 0; j < NREG / 4; ++j) {
-                    const int n = 4 * (s + RC_NS * j);
-                    if (n < N) {
-                        const float4 bv = *reinterpret_cast<const float4*>(Bt + n);
-                        const float4 cv = *reinterpret_cast<const float4*>(Ct + n);
-                        S[4 * j] = fmaf(da, S[4 * j], dtx * bv.x);
-                        S[4 * j + 1] = fmaf(da, S[4 * j + 1], dtx * bv.y);
-                        S[4 * j + 2] = fmaf(da, S[4 * j + 2], dtx * bv.z);
-                        S[4 * j + 3] = fmaf(da, S[4 * j + 3], dtx * bv.w);
-                        acc = fmaf(S[4 * j], cv.x, acc);
-                        acc = fmaf(S[4 * j + 1], cv.y, acc);
-                        acc = fmaf(S[4 * j + 2], cv.z, acc);
-                        acc = fmaf(S[4 * j + 3], cv.w, acc);
-                    }
-                }
-            } else {
-#pragma unroll
-                for (int r = 0; r < NREG; ++r) {
-                    const int n = s + RC_NS * r;
-                    if (n < N) {
-                        S[r] = fmaf(da, S[r], dtx * Bt[n]);
-                        acc = fmaf(S[r], Ct[n], acc);
-                    }
-                }
-            }
-            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-            if (s == 0 && p_ok)
-                a.y[(size_t)(t0 + c0 + tt) * inner + h * P + p] = fmaf(dsk, xv, acc);
-        }
+        const float* xs = rc_smem + buf * buf_floats;
+        const float* Bs = xs + RC_TC * RC_PB;
+        const float* Cs = Bs + RC_TC * N;
+        // RC_TU tokens an iteration: a token's chain (products, the eight threads' sums by
+        // shuffles, the store) is long and the next token only waits for S, so the chains of
+        // RC_TU tokens are issued side by side; the tokens left over go one by one
+        int tt = 0;
+        for (; tt + RC_TU <= nc; tt += RC_TU)
+            rc_walk<NREG, VEC, RC_TU, NS>(S, xs, Bs, Cs, dts + buf * RC_TC, das + buf * RC_TC, tt, N, s, pl, p_ok,
+                                      dsk, a.y + (size_t)(t0 + c0) * inner + h * P + p, inner);
+        for (; tt < nc; ++tt)
+            rc_walk<NREG, VEC, 1, NS>(S, xs, Bs, Cs, dts + buf * RC_TC, das + buf * RC_TC, tt, N, s, pl, p_ok,
+                                  dsk, a.y + (size_t)(t0 + c0) * inner + h * P + p, inner);
+        __syncthreads();                          // the buffer may be refilled now
     }
     if (p_ok) {
         if (VEC) {
 #pragma unroll
             for (int j = 0; j < NREG / 4; ++j) {
-                const int n = 4 * (s + RC_NS * j);
+                const int n = 4 * (s + NS * j);
                 if (n < N)
                     *reinterpret_cast<float4*>(st + n) =
                         make_float4(S[4 * j], S[4 * j + 1], S[4 * j + 2], S[4 * j + 3]);
@@ -333,28 +412,33 @@ extern "C" int mf_ssm_scan(const float* u, const float* proj, long long in_width
     a.cu_seqlens = cu_seqlens; a.slots = slots; a.y = y; a.heads = heads; a.P = P; a.N = N;
     a.groups = groups;
     const int pb = P < RC_PB ? P : RC_PB;
-    dim3 grid(n_rows, heads, (P + RC_PB - 1) / RC_PB), block(((pb * RC_NS + 31) / 32) * 32);
-    const size_t smem = (size_t)(RC_TC * (RC_PB + 2 * N + 2)) * sizeof(float);
-    // float4 groups need rows of B, C and the state on 16-byte boundaries
-    const bool vec = N % 4 == 0 && ((uintptr_t)state & 15) == 0;
-    const int nreg = vec ? 4 * ((N / 4 + RC_NS - 1) / RC_NS) : (N + RC_NS - 1) / RC_NS;
-#define MF_SCAN(NR, V) \
+    // float4 groups need rows of B, C (in shared memory) and of the state on 16-byte boundaries
+    const bool vec = N % 4 == 0 && ((uintptr_t)state & 15) == 0 && ((uintptr_t)u & 15) == 0;
+    // threads that share a column: 16 for wide states (twice the warps on an SM, which the
+    // chains of dependent shared-memory loads, products and shuffles need), else 8
+    const int ns = (vec && N >= 128) ? 16 : RC_NS;
+    dim3 grid(n_rows, heads, (P + RC_PB - 1) / RC_PB), block(((pb * ns + 31) / 32) * 32);
+    const size_t smem = (size_t)(2 * RC_TC * (RC_PB + 2 * N + 2)) * sizeof(float);
+    const int nreg = vec ? 4 * ((N / 4 + ns - 1) / ns) : (N + ns - 1) / ns;
+#define MF_SCAN(NR, V, S_) \
     do { \
         if (smem > 48 * 1024) \
-            cudaFuncSetAttribute(ssm_scan_kernel<NR, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        mf_launch(ssm_scan_kernel<NR, V>, grid, block, smem, stream, a); \
+            cudaFuncSetAttribute(ssm_scan_kernel<NR, V, S_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        mf_launch(ssm_scan_kernel<NR, V, S_>, grid, block, smem, stream, a); \
     } while (0)
-    if (vec) {
-        if (nreg <= 4) MF_SCAN(4, true);
-        else if (nreg <= 8) MF_SCAN(8, true);
-        else if (nreg <= 16) MF_SCAN(16, true);
-        else MF_SCAN(32, true);
+    if (vec && ns == 16) {
+        if (nreg <= 8) MF_SCAN(8, true, 16);
+        else MF_SCAN(16, true, 16);
+    } else if (vec) {
+        if (nreg <= 4) MF_SCAN(4, true, 8);
+        else if (nreg <= 8) MF_SCAN(8, true, 8);
+        else MF_SCAN(16, true, 8);
     } else {
-        if (nreg <= 2) MF_SCAN(2, false);
-        else if (nreg <= 4) MF_SCAN(4, false);
-        else if (nreg <= 8) MF_SCAN(8, false);
-        else if (nreg <= 16) MF_SCAN(16, false);
-        else MF_SCAN(32, false);
+        if (nreg <= 2) MF_SCAN(2, false, 8);
+        else if (nreg <= 4) MF_SCAN(4, false, 8);
+        else if (nreg <= 8) MF_SCAN(8, false, 8);
+        else if (nreg <= 16) MF_SCAN(16, false, 8);
+        else MF_SCAN(32, false, 8);
     }
 #undef MF_SCAN
     return MF_LAUNCH_CHECK();

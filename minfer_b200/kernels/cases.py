@@ -457,13 +457,89 @@ def step_decode_small(reps, layers=24):
     print(f"decode step, small shape, {layers} layers, batch 64 ragged: {us:.1f} us")
 
 
+# ---- the state-space recurrence and the steps of a model with three kinds of mixer ---------------
+def _ssm_inputs(n, rows, heads=64, head_dim=64, n_state=128):
+    inner, ch = heads * head_dim, heads * head_dim + 2 * n_state
+    proj = torch.randn(n, 2 * inner + 2 * n_state + heads, device="cuda")
+    u = torch.randn(n, ch, device="cuda") * 0.3
+    state = torch.zeros(rows + 1, heads, head_dim, n_state, device="cuda")
+    y = torch.empty(n, inner, device="cuda")
+    z = torch.zeros(heads, device="cuda")
+    cu = torch.arange(rows + 1, dtype=torch.int32, device="cuda") * (n // rows)
+    slots = torch.arange(rows, dtype=torch.int32, device="cuda")
+    return (lambda: K.ssm_scan(u, proj, inner + ch, z, z, z, state, cu, slots, y, rows, heads, head_dim,
+                               n_state, 1)), n * (ch + inner + heads) * 4 + rows * heads * head_dim * n_state * 8
+
+
+def ssm_scan_prompt(reps, tokens=2048):
+    """The recurrence over one prompt of 2,048 tokens: 64 heads of 64 columns, state of 128."""
+    run, nbytes = _ssm_inputs(tokens, 1)
+    us = _time(run, reps)
+    print(f"ssm_scan, {tokens} tokens of one sequence: {us:.1f} us, {nbytes / us / 1e3:.0f} GB/s of "
+          f"inputs, outputs and state")
+
+
+def ssm_scan_decode(reps, batch=64):
+    """The recurrence for one token of each of 64 sequences (the state read and written once)."""
+    run, nbytes = _ssm_inputs(batch, batch)
+    us = _time(run, reps)
+    print(f"ssm_scan, one token of {batch} sequences: {us:.1f} us, {nbytes / us / 1e3:.0f} GB/s")
+
+
+def _budanex_engine(max_tokens=8 * 4096, max_seqs=8):
+    from ..engine.step import Engine
+    from ..model import Model
+    mamba = {"type": "mamba2", "mlp": None,
+             "mixer": {"heads": 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1}}
+    latent = {"type": "latent_attention", "mlp": {"kind": "dense", "ff": 5632},
+              "mixer": {"heads": 16, "dim": 64, "rot_dim": 32, "vdim": 64, "kv_rank": 96,
+                        "scale": 96 ** -0.5, "mask": {"size": 1024},
+                        "rot": {"base": 500000.0, "dims": 32,
+                                "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    attention = {"type": "attention", "mlp": {"kind": "dense", "ff": 5632},
+                 "mixer": {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                           "softcap": 50.0, "rot": {"base": 1000000.0, "dims": 64}}}
+    cfg = {"architecture": "Budanex", "vocab": 32000, "width": 2048, "norm": {"eps": 1e-5},
+           "logit_softcap": 30.0, "loop": {"start": 0, "stop": 3, "times": 2},
+           "layers": [mamba, latent, attention]}
+    model = Model.from_config(cfg, seed=0, dtype="bfloat16", device="cuda:0", make_on="device")
+    return Engine(model, max_tokens=max_tokens, max_seqs=max_seqs, cuda_graphs=False), cfg
+
+
+def budanex_step_prefill(reps, tokens=2048):
+    """A whole prompt of 2,048 tokens through a Budanex model of width 2,048: a state-space, a
+    latent-attention and an attention layer, run twice (six layer runs), plus the head."""
+    eng, cfg = _budanex_engine()
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, cfg["vocab"], (tokens,), generator=g).tolist()
+
+    def run():
+        s = eng.acquire()
+        eng.step([s], [ids])
+        eng.release(s)
+    us = _time(run, reps, graph=False)
+    print(f"budanex prefill step, {tokens} tokens, six layer runs: {us:.1f} us")
+
+
+def budanex_step_decode(reps, batch=8, ctx=2048):
+    """Decode steps of 8 sequences at 2,048 positions through the same model, kernel by kernel."""
+    eng, cfg = _budanex_engine()
+    g = torch.Generator().manual_seed(0)
+    slots = [eng.acquire() for _ in range(batch)]
+    eng.step(slots, [torch.randint(0, cfg["vocab"], (ctx,), generator=g).tolist() for _ in range(batch)])
+    tokens = torch.randint(0, cfg["vocab"], (batch,), dtype=torch.int32, device="cuda")
+    us = _time(lambda: eng.decode_on_device(slots, tokens), reps, graph=False)
+    print(f"budanex decode step, batch {batch} at {ctx} positions, six layer runs: {us:.1f} us")
+
+
 CASES = {f.__name__: f for f in (gemm_decode, gemm_decode_split, gemm_decode_m64, gemm_decode_split_m64, gemm_prefill, gemm_prefill_down,
                                  gemm_decode_cluster, gemm_decode_cluster_o, gemm_decode_cluster_m64,
                                  attention_decode, attention_decode_b8, attention_decode_long, attention_prefill,
                                  attention_prefill_tc, attention_prefill_tc_8k, attention_prefill_8k,
                                  attention_portion, attention_portion_512_on_8k,
                                  step_prefill, step_prefill_timeline, step_portions, step_decode, step_decode_sweep, step_prefill_sweep, step_decode_timeline,
-                                 step_decode_timeline_b64, step_decode_b64, step_decode_small)}
+                                 step_decode_timeline_b64, step_decode_b64, step_decode_small,
+                                 ssm_scan_prompt, ssm_scan_decode, budanex_step_prefill, budanex_step_decode)}
 
 
 def main(argv=None) -> int:

@@ -204,3 +204,88 @@ def test_greedy_generation_through_the_generator(case, dtype):
                 slack = 2 * TOL["bfloat16"] * float(logits.abs().max())
                 assert float(logits[tok]) >= float(logits.max()) - slack
             ids.append(tok)
+
+
+def test_command_line_generates(capsys):
+    from minfer_b200 import cli
+    folder = make_folder("B")
+    cfg, w = P.load_folder(folder)
+    rc = cli.main([folder, "5,17,3", "--greedy", "--repeat-penalty", "1.0", "-n", "6",
+                   "--dtype", "float32", "--stop", "100000"])
+    out = capsys.readouterr().out
+    assert rc == 0
+    want = P.generate_greedy(cfg, w, [5, 17, 3], 6)
+    assert " ".join(str(t) for t in want) in out
+    assert "Prefill: 3 tokens" in out and "Generated: 6 tokens" in out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_replay_as_a_process(dtype):
+    """``bin/trace_run`` on a Budanex folder: two prompts of unequal length in one step, then one
+    request's last tokens one by one beside another that ends earlier; logits files against the
+    plain implementation."""
+    import json
+    import os
+    import subprocess
+    import sys
+    import tempfile
+    import numpy as np
+    folder = make_folder("A")
+    cfg, w = P.load_folder(folder)
+    a, b = random_ids(70, cfg["vocab"], 1), random_ids(9, cfg["vocab"], 2)
+    plain = {"a": P.forward(cfg, w, a), "b": P.forward(cfg, w, b)}
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:60], "want": [0, 59]},
+                                     {"id": "b", "tokens": b[:7], "want": [6]}], "end": []}]
+    expect = {0: [("a", [0, 59]), ("b", [6])]}
+    for i in range(10):
+        entries = [{"id": "a", "tokens": [a[60 + i]], "want": [0] if i % 2 == 0 else []}]
+        rows = [("a", [60 + i])] if i % 2 == 0 else []
+        if i < 2:
+            entries.append({"id": "b", "tokens": [b[7 + i]], "want": [0]})
+            rows.append(("b", [7 + i]))
+        end = (["b"] if i == 1 else []) + (["a"] if i == 9 else [])
+        steps.append({"step": i + 1, "entries": entries, "end": end})
+        expect[i + 1] = rows
+    out = tempfile.mkdtemp()
+    root = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..")
+    proc = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", folder,
+                           "--dtype", dtype, "--out", out, "--max-tokens", "128"],
+                          input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True,
+                          text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(11)]
+    for step, rows in expect.items():
+        path = os.path.join(out, f"{step}.f32")
+        if not rows:
+            assert not os.path.exists(path)
+            continue
+        got = torch.from_numpy(np.fromfile(path, dtype="<f4").reshape(-1, cfg["vocab"]))
+        want = torch.cat([plain[r][places] for r, places in rows])
+        _close(got, want, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_model_of_state_space_layers_only(dtype):
+    """No attention anywhere: the cache has no page group at all, only state."""
+    import copy
+    import tempfile
+    from budanex_cases import BUD_A
+    from minfer_b200.model import write_random_model
+    cfg = copy.deepcopy(BUD_A)
+    cfg["layers"] = [cfg["layers"][1], cfg["layers"][3]]
+    cfg["loop"] = {"start": 1, "stop": 2, "times": 2}
+    folder = tempfile.mkdtemp(prefix="minfer_b200_bud_ssm_")
+    write_random_model(folder, cfg, 31, "bfloat16", norm_std=0.05, weight_std=0.08)
+    cfg, w = P.load_folder(folder)
+    ids = random_ids(90, cfg["vocab"], 4)
+    want = P.forward(cfg, w, ids)
+    eng = _engine(folder, dtype, max_tokens=512)
+    assert not eng.cache.groups
+    s = eng.acquire()
+    rows = [eng.step([s], [ids[:50]], [list(range(50))])]
+    rows.append(eng.step([s], [ids[50:53]], [[0, 1, 2]]))
+    for t in range(53, 90):
+        rows.append(eng.step([s], [[ids[t]]], [[0]]))
+    eng.release(s)
+    _close(torch.cat(rows), want, dtype)
+    eng.check_status()

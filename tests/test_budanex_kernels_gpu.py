@@ -231,7 +231,7 @@ def _mamba_setup(seed, heads, P_, N, groups, taps, norm_groups, width=48):
 
 
 @pytest.mark.parametrize("sizes", [(4, 8, 16, 2, 4, 2), (3, 20, 24, 1, 3, 1), (6, 5, 7, 6, 1, 3),
-                                   (2, 70, 130, 2, 8, 4), (8, 64, 128, 1, 4, 1)])
+                                   (2, 70, 130, 2, 8, 4), (8, 64, 128, 1, 4, 1), (2, 16, 256, 1, 2, 1)])
 @pytest.mark.parametrize("cuts", [[200], [1] * 40, [2] * 30, [3, 1, 2, 64, 65, 1, 7], [150, 2, 1, 1, 46]])
 def test_state_space_kernels_over_cuts(sizes, cuts):
     """Convolution, recurrence and gated norm as the mixer chains them, a sequence fed in cuts of

@@ -414,9 +414,11 @@ extern "C" int mf_ssm_scan(const float* u, const float* proj, long long in_width
     const int pb = P < RC_PB ? P : RC_PB;
     // float4 groups need rows of B, C (in shared memory) and of the state on 16-byte boundaries
     const bool vec = N % 4 == 0 && ((uintptr_t)state & 15) == 0 && ((uintptr_t)u & 15) == 0;
-    // threads that share a column: 16 for wide states (twice the warps on an SM, which the
-    // chains of dependent shared-memory loads, products and shuffles need), else 8
-    const int ns = (vec && N >= 128) ? 16 : RC_NS;
+    // threads that share a column: 8.  (16 for states of 128 and more, twice the warps on an SM,
+    // measured: one prompt of 2,048 tokens 583 -> 549 us with 64 heads, but 780 -> 1,081 us with
+    // 128 heads and single tokens 16 -> 25 us: more instructions in all, and once every SM has
+    // two blocks the kernel is bound by issue slots, not by latency.  The form stays compiled.)
+    const int ns = RC_NS;
     dim3 grid(n_rows, heads, (P + RC_PB - 1) / RC_PB), block(((pb * ns + 31) / 32) * 32);
     const size_t smem = (size_t)(2 * RC_TC * (RC_PB + 2 * N + 2)) * sizeof(float);
     const int nreg = vec ? 4 * ((N / 4 + ns - 1) / ns) : (N + ns - 1) / ns;

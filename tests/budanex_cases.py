@@ -64,7 +64,17 @@ BUD_C = {
                              {"factor": 4.0, "original": 128, "fast": 32.0, "slow": 1.0}), 256),
                _with(_attention(4, 1, 64, 128, 0.125, 40.0, 32, 1000000.0), 256)],
 }
-CASES = {"A": (BUD_A, 21), "B": (BUD_B, 22), "C": (BUD_C, 23)}
+# keys and values of one size the tensor-memory kernel takes, in both attention mixers (128 with a
+# soft cap; a latent of 48 + 16); one pass of a loop over all layers; a single key/value head
+BUD_D = {
+    "architecture": "Budanex", "vocab": 173, "width": 128, "norm": {"eps": 1e-6},
+    "logit_softcap": 12.0, "loop": {"start": 0, "stop": 3, "times": 1},
+    "layers": [_with(_attention(2, 1, 128, 128, 0.09, 15.0, 128, 500000.0), 192),
+               _with(_latent(4, 24, 16, 40, 48, 0.18, 150,
+                             {"factor": 16.0, "original": 256, "fast": 64.0, "slow": 4.0}, 10000.0)),
+               _with(_mamba(2, 32, 64, 1, 4, 2), 160)],
+}
+CASES = {"A": (BUD_A, 21), "B": (BUD_B, 22), "C": (BUD_C, 23), "D": (BUD_D, 24)}
 
 
 def make_folder(name: str) -> str:

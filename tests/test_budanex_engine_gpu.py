@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 LENGTHS = [37, 5, 131, 64, 1, 65, 11]
 
 
-@pytest.fixture(scope="module", params=["A", "B", "C"])
+@pytest.fixture(scope="module", params=["A", "B", "C", "D"])
 def case(request):
     folder = make_folder(request.param)
     cfg, w = P.load_folder(folder)
@@ -181,6 +181,33 @@ def test_long_decoding_past_the_rings(name, dtype):
     eng.check_status()
     eng2.check_status()
     eng2.cache.check_canaries()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["C", "D"])
+def test_a_long_prompt_in_large_portions(name, dtype):
+    """430 tokens in portions of 200, 220 and 10: the later portions are query tiles over the
+    cache's pages (the tensor-memory kernel where keys and values have one size), across the
+    window's edge; then the same prompt whole beside a short one."""
+    folder = make_folder(name)
+    cfg, w = P.load_folder(folder)
+    ids = random_ids(430, cfg["vocab"], 17)
+    want = P.forward(cfg, w, ids)
+    eng = _engine(folder, dtype, max_tokens=2048)
+    s = eng.acquire()
+    rows, at = [], 0
+    for n in (200, 220, 10):
+        rows.append(eng.step([s], [ids[at:at + n]], [list(range(n))]))
+        at += n
+    eng.release(s)
+    _close(torch.cat(rows), want, dtype)
+    short = random_ids(33, cfg["vocab"], 18)
+    a, b = eng.acquire(), eng.acquire()
+    out = eng.step([b, a], [short, ids], [[32], [429, 0, 215]])
+    _close(out[0:1], P.forward(cfg, w, short)[32:33], dtype)
+    _close(out[1:4], want[[429, 0, 215]], dtype)
+    eng.check_status()
+    eng.cache.check_canaries()
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

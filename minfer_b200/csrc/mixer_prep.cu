@@ -161,7 +161,6 @@ extern "C" int mf_qk_prepare(const PrepArgs* args, int n_tokens, int dtype, cuda
     if (!a.v_from_k && (a.k_cache == nullptr) != (a.v_cache == nullptr)) return MF_ERR_ARGUMENT;
     if (a.k_cache != nullptr && a.page_table == nullptr) return MF_ERR_ARGUMENT;
     if (a.v_from_k && a.vw > a.kw) return MF_ERR_ARGUMENT;
-    // a rotated pair must lie wholly inside or wholly outside the normed stretch of its segment
     const size_t smem = (size_t)(a.rot_dims > 0 ? a.rot_dims : 2) * sizeof(float);
     // few tokens: a token's elements are spread over up to 8 blocks
     int by = 1;

@@ -179,10 +179,10 @@ extern "C" int mf_conv_silu(const float* proj, long long in_width, int x_off, in
 // the recurrence
 // ------------------------------------------------------------------------------------------
 // A block owns one head of one row and up to RC_PB of its P columns.  NS = 8 or 16 threads share a
-// column p: thread (p, s) keeps NREG elements of the column's state in registers, and the eight
+// column p: thread (p, s) keeps NREG elements of the column's state in registers, and the NS
 // partial sums of y meet by shuffles.  Which elements: with VEC (N a multiple of 4) the float4
-// groups s, s + 8, s + 16, .. (n = 4 (s + 8 j) + e), else the single elements s, s + 8, ..
-// (n = s + 8 r): either way the eight threads of a column read consecutive words of B and C in
+// groups s, s + NS, s + 2 NS, .. (n = 4 (s + NS j) + e), else the single elements s, s + NS, ..
+// (n = s + NS r): either way the threads of a column read consecutive words of B and C in
 // shared memory (no bank conflicts; the other columns' threads read the same words) and
 // consecutive words of the state in memory.  Tokens come in chunks of RC_TC through two buffers in
 // shared memory filled by cp.async: the next chunk travels while this one is walked.
@@ -217,7 +217,7 @@ __device__ __forceinline__ void rc_cp_async16(float* dst, const float* src) {
 #define RC_TU 4
 
 // TU consecutive tokens of a chunk, from token `tt` on: S <- da S + dt x B, y = S . C + D x for
-// each in turn (S carries over), the TU sums reduced over a column's eight threads together.
+// each in turn (S carries over), the TU sums reduced over a column's NS threads together.
 template <int NREG, bool VEC, int TU, int NS>
 __device__ __forceinline__ void rc_walk(float (&S)[NREG], const float* xs, const float* Bs, const float* Cs,
                                         const float* dts, const float* das, int tt, int N, int s, int pl,
@@ -369,7 +369,7 @@ __global__ void __launch_bounds__(RC_PB * NS) ssm_scan_kernel(ScanArgs a) {
         const float* xs = rc_smem + buf * buf_floats;
         const float* Bs = xs + RC_TC * RC_PB;
         const float* Cs = Bs + RC_TC * N;
-        // RC_TU tokens an iteration: a token's chain (products, the eight threads' sums by
+        // RC_TU tokens an iteration: a token's chain (products, the column's threads' sums by
         // shuffles, the store) is long and the next token only waits for S, so the chains of
         // RC_TU tokens are issued side by side; the tokens left over go one by one
         int tt = 0;
@@ -434,7 +434,8 @@ extern "C" int mf_ssm_scan(const float* u, const float* proj, long long in_width
     } else if (vec) {
         if (nreg <= 4) MF_SCAN(4, true, 8);
         else if (nreg <= 8) MF_SCAN(8, true, 8);
-        else MF_SCAN(16, true, 8);
+        else if (nreg <= 16) MF_SCAN(16, true, 8);
+        else MF_SCAN(32, true, 8);
     } else {
         if (nreg <= 2) MF_SCAN(2, false, 8);
         else if (nreg <= 4) MF_SCAN(4, false, 8);

@@ -274,7 +274,10 @@ __device__ __forceinline__ void rc_walk(float (&S)[NREG], const float* xs, const
 
 template <int NREG, bool VEC, int NS>
 __global__ void __launch_bounds__(RC_PB * NS) ssm_scan_kernel(ScanArgs a) {
-    pdl_launch_dependents();
+    // (the kernel behind this one is let in only after the walk, further down: a block here runs
+    // for as long as its row is, and blocks of the next kernel that wait beside it on the same SM
+    // slowed it down: a prompt of 2,048 tokens through six layer runs 3.54 ms against 2.89 ms
+    // without early launches)
     extern __shared__ __align__(16) float rc_smem[];
     const int b = blockIdx.x, h = blockIdx.y, p0 = blockIdx.z * RC_PB;
     const int tid = threadIdx.x, s = tid & (NS - 1), pl = tid / NS;
@@ -381,6 +384,7 @@ __global__ void __launch_bounds__(RC_PB * NS) ssm_scan_kernel(ScanArgs a) {
                                   dsk, a.y + (size_t)(t0 + c0) * inner + h * P + p, inner);
         __syncthreads();                          // the buffer may be refilled now
     }
+    pdl_launch_dependents();
     if (p_ok) {
         if (VEC) {
 #pragma unroll
@@ -401,9 +405,9 @@ __global__ void __launch_bounds__(RC_PB * NS) ssm_scan_kernel(ScanArgs a) {
 extern "C" int mf_ssm_scan(const float* u, const float* proj, long long in_width, int dt_off,
                            int channels, const float* dt_bias, const float* a_log,
                            const float* d_skip, float* state, const int* cu_seqlens,
-                           const int* slots, float* y, int n_rows, int heads, int P, int N,
-                           int groups, cudaStream_t stream) {
-    if (n_rows <= 0) return 0;
+                           const int* slots, float* y, int n_tokens, int n_rows, int heads, int P,
+                           int N, int groups, cudaStream_t stream) {
+    if (n_rows <= 0 || n_tokens <= 0) return 0;
     if (heads < 1 || P < 1 || N < 1 || N > RC_NS * 32) return MF_ERR_UNSUPPORTED;
     if (groups < 1 || heads % groups != 0) return MF_ERR_ARGUMENT;
     ScanArgs a;
@@ -414,13 +418,33 @@ extern "C" int mf_ssm_scan(const float* u, const float* proj, long long in_width
     const int pb = P < RC_PB ? P : RC_PB;
     // float4 groups need rows of B, C (in shared memory) and of the state on 16-byte boundaries
     const bool vec = N % 4 == 0 && ((uintptr_t)state & 15) == 0 && ((uintptr_t)u & 15) == 0;
-    // threads that share a column: 8.  (16 for states of 128 and more, twice the warps on an SM,
-    // measured: one prompt of 2,048 tokens 583 -> 549 us with 64 heads, but 780 -> 1,081 us with
-    // 128 heads and single tokens 16 -> 25 us: more instructions in all, and once every SM has
-    // two blocks the kernel is bound by issue slots, not by latency.  The form stays compiled.)
-    const int ns = RC_NS;
+    // threads that share a column: 8; 16 for states of 128 and more when rows are long and the
+    // grid gives an SM one block at most (one prompt on few heads): the kernel then waits on its
+    // chains of dependent loads, products and shuffles, and twice the warps hide more of them.
+    // With more blocks an SM it is bound by issue slots, and 16 threads a column execute more
+    // instructions in all.  Measured inside a model's step (width 2,048 / 4,096: 64 / 128 heads
+    // of 64 columns, state 128), 8 -> 16: a prompt of 2,048 tokens 4.48 -> 4.38 ms and 8.19 ->
+    // 9.13 ms, a decode step of 8 sequences 0.639 -> 0.663 ms and 1.022 -> 1.078 ms.
+    // MINFER_B200_SCAN_THREADS=8|16 forces one form (for comparison).
+    static int forced = -1;
+    if (forced < 0) { const char* e = getenv("MINFER_B200_SCAN_THREADS"); forced = e ? atoi(e) : 0; }
+    const long long n_blocks = (long long)n_rows * heads * ((P + RC_PB - 1) / RC_PB);
+    int ns = (vec && N >= 128 && (long long)n_tokens >= 64LL * n_rows && n_blocks <= mf_sm_count()) ? 16 : RC_NS;
+    if (vec && N >= 64 && (forced == 8 || forced == 16)) ns = forced;
     dim3 grid(n_rows, heads, (P + RC_PB - 1) / RC_PB), block(((pb * ns + 31) / 32) * 32);
-    const size_t smem = (size_t)(2 * RC_TC * (RC_PB + 2 * N + 2)) * sizeof(float);
+    size_t smem = (size_t)(2 * RC_TC * (RC_PB + 2 * N + 2)) * sizeof(float);
+    // A block runs for as long as its row is, so the blocks must lie evenly over the SMs.  Launched
+    // early (programmatic dependent launch), they are placed while the kernel before still holds
+    // most SMs, and several land on one SM although others will be free in a moment (a prompt of
+    // 2,048 tokens through six layer runs: 3.5 ms against 2.9 ms without early launches).  So a
+    // block asks for so much shared memory that no SM takes more than its even share.
+    {
+        const long long blocks = (long long)n_rows * heads * ((P + RC_PB - 1) / RC_PB);
+        const long long share = (blocks + mf_sm_count() - 1) / mf_sm_count();       // blocks an SM, evenly
+        const size_t most = 227 * 1024;                // shared memory of an SM that blocks can have
+        const size_t pad = most / (size_t)(share + 1) + 1024;
+        if (pad > smem && pad <= most - 1024) smem = pad;
+    }
     const int nreg = vec ? 4 * ((N / 4 + ns - 1) / ns) : (N + ns - 1) / ns;
 #define MF_SCAN(NR, V, S_) \
     do { \

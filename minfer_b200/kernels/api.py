@@ -198,7 +198,7 @@ def _sig_recurrent(lib: ctypes.CDLL) -> None:
     lib.mf_conv_silu.argtypes = ([c_void_p, c_longlong, c_int, c_int, c_int] + [c_void_p] * 7 +
                                  [c_int, c_int, c_int, c_void_p])
     lib.mf_ssm_scan.argtypes = ([c_void_p, c_void_p, c_longlong, c_int, c_int] + [c_void_p] * 7 +
-                                [c_int] * 5 + [c_void_p])
+                                [c_int] * 6 + [c_void_p])
     lib.mf_gated_group_norm.argtypes = [c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p,
                                         c_int, c_int, c_int, c_int, c_float, c_void_p]
 
@@ -818,7 +818,7 @@ def ssm_scan(u: torch.Tensor, proj: torch.Tensor, dt_off: int, dt_bias: torch.Te
     _check(_lib("recurrent").mf_ssm_scan(
         _f32(u, "u"), _f32(proj, "proj"), proj.shape[1], int(dt_off), u.shape[1],
         _f32(dt_bias, "dt_bias"), _f32(a_log, "a_log"), _f32(d_skip, "d_skip"), _f32(state, "state"),
-        _i32(cu_seqlens, "cu_seqlens"), _i32(slots, "slots"), _f32(y, "y"), int(n_rows), heads,
+        _i32(cu_seqlens, "cu_seqlens"), _i32(slots, "slots"), _f32(y, "y"), n, int(n_rows), heads,
         head_dim, n_state, groups, _stream()), "ssm_scan")
 
 

@@ -500,15 +500,16 @@ def _budanex_engine(max_tokens=8 * 4096, max_seqs=8):
                  "mixer": {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
                            "softcap": 50.0, "rot": {"base": 1000000.0, "dims": 64}}}
     cfg = {"architecture": "Budanex", "vocab": 32000, "width": 2048, "norm": {"eps": 1e-5},
-           "logit_softcap": 30.0, "loop": {"start": 0, "stop": 3, "times": 2},
-           "layers": [mamba, latent, attention]}
+           "logit_softcap": 30.0, "loop": {"start": 3, "stop": 6, "times": 2},
+           "layers": [mamba, latent, attention, mamba, latent, attention]}
     model = Model.from_config(cfg, seed=0, dtype="bfloat16", device="cuda:0", make_on="device")
     return Engine(model, max_tokens=max_tokens, max_seqs=max_seqs, cuda_graphs=False), cfg
 
 
 def budanex_step_prefill(reps, tokens=2048):
-    """A whole prompt of 2,048 tokens through a Budanex model of width 2,048: a state-space, a
-    latent-attention and an attention layer, run twice (six layer runs), plus the head."""
+    """A whole prompt of 2,048 tokens through a Budanex model of width 2,048: six layers
+    [state-space, latent attention, attention] x 2, the last three run twice (nine layer runs),
+    plus the head."""
     eng, cfg = _budanex_engine()
     g = torch.Generator().manual_seed(0)
     ids = torch.randint(0, cfg["vocab"], (tokens,), generator=g).tolist()
@@ -518,7 +519,7 @@ def budanex_step_prefill(reps, tokens=2048):
         eng.step([s], [ids])
         eng.release(s)
     us = _time(run, reps, graph=False)
-    print(f"budanex prefill step, {tokens} tokens, six layer runs: {us:.1f} us")
+    print(f"budanex prefill step, {tokens} tokens, nine layer runs: {us:.1f} us")
 
 
 def budanex_step_decode(reps, batch=8, ctx=2048):
@@ -529,7 +530,7 @@ def budanex_step_decode(reps, batch=8, ctx=2048):
     eng.step(slots, [torch.randint(0, cfg["vocab"], (ctx,), generator=g).tolist() for _ in range(batch)])
     tokens = torch.randint(0, cfg["vocab"], (batch,), dtype=torch.int32, device="cuda")
     us = _time(lambda: eng.decode_on_device(slots, tokens), reps, graph=False)
-    print(f"budanex decode step, batch {batch} at {ctx} positions, six layer runs: {us:.1f} us")
+    print(f"budanex decode step, batch {batch} at {ctx} positions, nine layer runs: {us:.1f} us")
 
 
 CASES = {f.__name__: f for f in (gemm_decode, gemm_decode_split, gemm_decode_m64, gemm_decode_split_m64, gemm_prefill, gemm_prefill_down,

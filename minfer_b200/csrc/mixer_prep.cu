@@ -14,7 +14,8 @@
 //                  places for such values may be null, for a caller that reads them from the keys.
 //   head_linear    y[t][h][j] = sum_d W[h][j][d] x[t][h][x_off + d] for every head h, optionally
 //                  times sigmoid(gate[t][h * J + j]), optionally followed by a copy of `tail`
-//                  elements x[t][h][x_tail_off ..] behind the J outputs.  float32 accumulation.
+//                  elements x[t][h][x_tail_off ..] behind the J outputs.  float32 accumulation;
+//                  bfloat16 on tensor cores (mma.sync), float32 on the FP32 pipe.
 #include "common.cuh"
 
 struct PrepArgs {
@@ -265,12 +266,124 @@ __global__ void __launch_bounds__(256) head_linear_kernel(HeadLinearArgs a) {
     }
 }
 
+// The same for bfloat16 on tensor cores: a block of four warps owns 64 tokens x 64 outputs of one
+// head, a warp 16 tokens x 64 outputs as eight m16n8k16 products per 16 elements of the reduction
+// (float32 accumulation).  x and W go through shared memory in chunks of HM_KC elements with rows
+// padded by 8 (fragments are read as 32-bit words without bank conflicts); elements beyond D, J or
+// the last token are zeros.
+#define HM_KC 64
+#define HM_LD (HM_KC + 8)
+
+__device__ __forceinline__ void hm_mma16816(float* d, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(128) head_linear_mma_kernel(HeadLinearArgs a) {
+    pdl_prologue();
+    __shared__ __align__(16) __nv_bfloat16 xs[64 * HM_LD];
+    __shared__ __align__(16) __nv_bfloat16 ws[64 * HM_LD];
+    const int h = blockIdx.z;
+    const int t0 = blockIdx.x * 64, j0 = blockIdx.y * 64;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const __nv_bfloat16* x = (const __nv_bfloat16*)a.x;
+    const __nv_bfloat16* w = (const __nv_bfloat16*)a.w + (size_t)h * a.J * a.D;
+    const __nv_bfloat16 zero = __float2bfloat16_rn(0.0f);
+    float acc[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f; }
+    // 16-byte copies where every row of x and of W starts on a 16-byte boundary
+    const bool vec = (a.x_row & 7) == 0 && (a.x_head & 7) == 0 && (a.x_off & 7) == 0 && (a.D & 7) == 0 &&
+                     (((uintptr_t)a.x | (uintptr_t)a.w) & 15) == 0;
+    for (int d0 = 0; d0 < a.D; d0 += HM_KC) {
+        if (vec) {
+            for (int i = tid; i < 64 * (HM_KC / 8); i += 128) {
+                const int r = i / (HM_KC / 8), d = (i - r * (HM_KC / 8)) * 8;
+                const int tok = t0 + r, j = j0 + r;
+                const bool d_ok = d0 + d < a.D;
+                uint4 xv = make_uint4(0u, 0u, 0u, 0u), wv = make_uint4(0u, 0u, 0u, 0u);
+                if (tok < a.n_tokens && d_ok)
+                    xv = *reinterpret_cast<const uint4*>(x + (size_t)tok * a.x_row + (size_t)h * a.x_head + a.x_off + d0 + d);
+                if (j < a.J && d_ok) wv = *reinterpret_cast<const uint4*>(w + (size_t)j * a.D + d0 + d);
+                *reinterpret_cast<uint4*>(xs + r * HM_LD + d) = xv;
+                *reinterpret_cast<uint4*>(ws + r * HM_LD + d) = wv;
+            }
+        } else {
+            for (int i = tid; i < 64 * HM_KC; i += 128) {
+                const int r = i / HM_KC, d = i - r * HM_KC;
+                const int tok = t0 + r, j = j0 + r;
+                const bool d_ok = d0 + d < a.D;
+                xs[r * HM_LD + d] = (tok < a.n_tokens && d_ok)
+                    ? x[(size_t)tok * a.x_row + (size_t)h * a.x_head + a.x_off + d0 + d] : zero;
+                ws[r * HM_LD + d] = (j < a.J && d_ok) ? w[(size_t)j * a.D + d0 + d] : zero;
+            }
+        }
+        __syncthreads();
+        const int k_end = min(HM_KC, ((a.D - d0 + 15) / 16) * 16);
+        for (int k0 = 0; k0 < k_end; k0 += 16) {
+            uint32_t af[4];
+            const __nv_bfloat16* xr = xs + (warp * 16 + g) * HM_LD + k0 + 2 * t;
+            af[0] = *reinterpret_cast<const uint32_t*>(xr);
+            af[1] = *reinterpret_cast<const uint32_t*>(xr + 8 * HM_LD);
+            af[2] = *reinterpret_cast<const uint32_t*>(xr + 8);
+            af[3] = *reinterpret_cast<const uint32_t*>(xr + 8 * HM_LD + 8);
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+                const __nv_bfloat16* wr = ws + (nt * 8 + g) * HM_LD + k0 + 2 * t;
+                hm_mma16816(acc[nt], af, *reinterpret_cast<const uint32_t*>(wr),
+                            *reinterpret_cast<const uint32_t*>(wr + 8));
+            }
+        }
+        __syncthreads();
+    }
+    __nv_bfloat16* y = (__nv_bfloat16*)a.y;
+    // a thread's two neighbouring outputs as one 4-byte store where they start on an even element
+    const bool pairs = (a.y_row & 1) == 0 && (a.y_head & 1) == 0 && (a.J & 1) == 0 && ((uintptr_t)a.y & 3) == 0;
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int tok = t0 + warp * 16 + g + half * 8;
+            const int j = j0 + nt * 8 + 2 * t;
+            if (tok >= a.n_tokens || j >= a.J) continue;
+            float v0 = acc[nt][2 * half], v1 = acc[nt][2 * half + 1];
+            if (a.gate) {
+                const float* gp = a.gate + (size_t)tok * a.gate_row + a.gate_off + (size_t)h * a.J + j;
+                v0 *= 1.0f / (1.0f + expf(-gp[0]));
+                if (j + 1 < a.J) v1 *= 1.0f / (1.0f + expf(-gp[1]));
+            }
+            __nv_bfloat16* dst = y + (size_t)tok * a.y_row + (size_t)h * a.y_head + j;
+            if (pairs) {
+                *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(v0, v1);
+            } else {
+                dst[0] = __float2bfloat16_rn(v0);
+                if (j + 1 < a.J) dst[1] = __float2bfloat16_rn(v1);
+            }
+        }
+    }
+    if (a.tail > 0 && blockIdx.y == 0) {
+        for (int i = tid; i < 64 * a.tail; i += 128) {
+            const int r = i / a.tail, d = i - r * a.tail;
+            const int tok = t0 + r;
+            if (tok < a.n_tokens)
+                y[(size_t)tok * a.y_row + (size_t)h * a.y_head + a.J + d] =
+                    x[(size_t)tok * a.x_row + (size_t)h * a.x_head + a.x_tail_off + d];
+        }
+    }
+}
+
 extern "C" int mf_head_linear(const HeadLinearArgs* args, int dtype, cudaStream_t stream) {
     const HeadLinearArgs a = *args;
     if (a.n_tokens <= 0) return 0;
     if (a.heads < 1 || a.J < 1 || a.D < 1 || a.tail < 0) return MF_ERR_ARGUMENT;
     dim3 grid((a.n_tokens + HL_TT - 1) / HL_TT, (a.J + HL_TJ - 1) / HL_TJ, a.heads);
+    static int simt = -1;              // MINFER_B200_HEAD_LINEAR=simt: the FP32-pipe kernel for bfloat16 too
+    if (simt < 0) { const char* e = getenv("MINFER_B200_HEAD_LINEAR"); simt = (e && e[0] == 's') ? 1 : 0; }
     if (dtype == MF_DTYPE_F32) mf_launch(head_linear_kernel<float>, grid, dim3(256), 0, stream, a);
+    else if (dtype == MF_DTYPE_BF16 && !simt) mf_launch(head_linear_mma_kernel, grid, dim3(128), 0, stream, a);
     else if (dtype == MF_DTYPE_BF16) mf_launch(head_linear_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, a);
     else return MF_ERR_UNSUPPORTED;
     return MF_LAUNCH_CHECK();

@@ -80,7 +80,8 @@ class LatentAttention(Mixer):
         self.sink_logit: Optional[torch.Tensor] = None
         self.uk_t: Optional[torch.Tensor] = None      # [heads, kv_rank, head_dim]: Wuk_h transposed
         self.uv: Optional[torch.Tensor] = None        # [heads, value_dim, kv_rank]
-        self._uk: Optional[torch.Tensor] = None       # as the checkpoint holds it
+        self._uk: Optional[torch.Tensor] = None       # as the checkpoint holds them
+        self._uv: Optional[torch.Tensor] = None
 
     def _widths(self):
         """Columns of the packed projection: q, latent, rotated key, gate."""
@@ -115,7 +116,8 @@ class LatentAttention(Mixer):
         self.sink_logit = weights[f"{p}sink"] if self.sink else None
         self._uk = weights[f"{p}uk"]
         self.uk_t = self._uk.view(self.n_heads, self.head_dim, self.kv_rank).transpose(1, 2).contiguous()
-        self.uv = weights[f"{p}uv"].view(self.n_heads, self.value_dim, self.kv_rank)
+        self._uv = weights[f"{p}uv"]
+        self.uv = self._uv.view(self.n_heads, self.value_dim, self.kv_rank)
         self.accepts_row_scale = self.proj.takes_row_scale()
 
     def export(self, prefix: str) -> Dict[str, torch.Tensor]:
@@ -123,7 +125,7 @@ class LatentAttention(Mixer):
         nq, rank, rd, ng = self._widths()
         w = self.proj.weight
         out = {f"{p}q": w[:nq], f"{p}dkv": w[nq:nq + rank + rd], f"{p}dkv.norm": self.c_norm,
-               f"{p}uk": self._uk, f"{p}uv": self.uv.view(self.n_heads * self.value_dim, rank),
+               f"{p}uk": self._uk, f"{p}uv": self._uv,
                f"{p}o": self.out.weight}
         if self.sink:
             out[f"{p}sink"] = self.sink_logit
@@ -178,6 +180,10 @@ class LatentAttention(Mixer):
                      v_off=0, v_width=rank, v_from_k=True, q_norm=None, k_norm=self.c_norm,
                      eps=self.norm_eps, inv_freq=inv_freq, rot_dims=rot_dims, rot_style=style,
                      rot_magnitude=magnitude, q_rot_off=hd, k_rot_off=rank, status=ctx.status)
+        if self.uk_t.dtype != act:
+            # (a checkpoint that stores its matrices in 32-bit keeps them so; the per-head products
+            # take operands of the activations' type)
+            self.uk_t, self.uv = self.uk_t.to(act), self.uv.to(act)
         # q'_h = [Wuk_h^T q_p | q_r]
         q_abs = torch.empty((n, nh * kw), dtype=act, device=dev)
         K.head_linear(q, self.uk_t, q_abs, x_head=hd + rd, x_off=0, y_head=kw, tail=rd, x_tail_off=hd)

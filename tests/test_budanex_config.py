@@ -101,3 +101,17 @@ def test_scaled_frequencies_follow_the_plain_ones():
     assert plain.magnitude() == 1.0
     assert torch.allclose(plain.inverse_frequencies(),
                           torch.tensor(P.plain_frequencies(8, 1e4), dtype=torch.float64), rtol=1e-14)
+
+
+def test_parts_export_what_they_loaded():
+    """Every tensor the model asks for comes back from ``export_state_dict`` under its name and
+    in its shape (packed projections as views), for all three configurations."""
+    for config in (BUD_A, BUD_B, BUD_C):
+        cfg = read_config(config)
+        model = Model(cfg.plan(), "float32", cfg)
+        weights = {s.name: torch.randn(s.shape, dtype=torch.float32) for s in model.tensor_specs()}
+        model.bind(weights, "cpu")
+        out = model.export_state_dict()
+        assert set(out) == set(weights)
+        for name, t in weights.items():
+            assert torch.equal(out[name], t), name

@@ -316,3 +316,23 @@ def test_a_model_of_state_space_layers_only(dtype):
     eng.release(s)
     _close(torch.cat(rows), want, dtype)
     eng.check_status()
+
+
+def test_matrices_stored_in_32_bit_run_in_the_bfloat16_engine():
+    """A checkpoint whose matrices are float32 keeps them so in the bfloat16 engine (FP32-pipe
+    products, bfloat16 cache and attention): every mixer takes the mix."""
+    import tempfile
+    from budanex_cases import BUD_A
+    from minfer_b200.model import write_random_model
+    folder = tempfile.mkdtemp(prefix="minfer_b200_bud32_")
+    write_random_model(folder, BUD_A, 41, "float32", norm_std=0.05, weight_std=0.08)
+    cfg, w = P.load_folder(folder)
+    ids = random_ids(75, cfg["vocab"], 8)
+    want = P.forward(cfg, w, ids)
+    eng = _engine(folder, "bfloat16", max_tokens=512)
+    s = eng.acquire()
+    rows = [eng.step([s], [ids[:60]], [list(range(60))])]
+    rows += [eng.step([s], [[t]], [[0]]) for t in ids[60:]]
+    eng.release(s)
+    _close(torch.cat(rows), want, "bfloat16")
+    eng.check_status()

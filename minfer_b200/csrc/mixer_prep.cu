@@ -152,6 +152,156 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(PrepArgs a) {
     }
 }
 
+// ---- the same with 16-byte accesses, for layouts in which every offset and width is a multiple of 4
+template <typename T> struct PrepStore4;
+template <> struct PrepStore4<float> {
+    static __device__ __forceinline__ void store(float* p, const float* v) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+};
+template <> struct PrepStore4<__nv_bfloat16> {
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* v) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+        uint2 u;
+        u.x = *reinterpret_cast<unsigned*>(&lo);
+        u.y = *reinterpret_cast<unsigned*>(&hi);
+        *reinterpret_cast<uint2*>(p) = u;
+    }
+};
+
+// four consecutive elements of a segment from element `e` on (a multiple of 4), after norm and
+// rotation, into out[0..3]
+__device__ __forceinline__ void prep_group(const float* seg, const float* norm_w, int norm_n, float rinv,
+                                           int d, int e, int rot_off, const PrepArgs& a, const float* cs,
+                                           float* out) {
+    auto load = [&](int at, float* v) {
+        const float4 x = *reinterpret_cast<const float4*>(seg + at);
+        v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+        if (at < norm_n) {
+            const float4 w = *reinterpret_cast<const float4*>(norm_w + at);
+            v[0] *= rinv * w.x; v[1] *= rinv * w.y; v[2] *= rinv * w.z; v[3] *= rinv * w.w;
+        }
+    };
+    float v[4];
+    load(e, v);
+    const int r = d - rot_off;
+    if (a.rot_dims <= 0 || r < 0 || r >= a.rot_dims) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) out[k] = v[k];
+        return;
+    }
+    if (a.rot_style == 0) {
+        const int half = a.rot_dims >> 1;
+        const bool first = r < half;
+        const int pair = first ? r : r - half;
+        float o[4];
+        load(first ? e + half : e - half, o);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float c = cs[2 * (pair + k)], sn = cs[2 * (pair + k) + 1];
+            out[k] = first ? v[k] * c - o[k] * sn : v[k] * c + o[k] * sn;
+        }
+    } else {
+        const int pair = r >> 1;
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const float c = cs[2 * (pair + k)], sn = cs[2 * (pair + k) + 1];
+            out[2 * k] = v[2 * k] * c - v[2 * k + 1] * sn;
+            out[2 * k + 1] = v[2 * k + 1] * c + v[2 * k] * sn;
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) qk_prepare_vec_kernel(PrepArgs a) {
+    pdl_launch_dependents();
+    extern __shared__ float pr_cs[];                  // [rot_dims / 2][2] cosine, sine
+    __shared__ float scratch[33];
+    const int t = blockIdx.x;
+    const int pos = a.positions[t];
+    const int b = a.token_row[t];
+    for (int i = threadIdx.x; i < (a.rot_dims >> 1); i += blockDim.x) {
+        double ang = (double)pos * a.inv_freq[i];
+        ang -= 6.283185307179586476925286766559 * floor(ang * 0.15915494309189533576888376337251);
+        float s, c;
+        sincosf((float)ang, &s, &c);
+        pr_cs[2 * i] = c * a.rot_mag;
+        pr_cs[2 * i + 1] = s * a.rot_mag;
+    }
+    int page = -1;
+    if (a.k_cache != nullptr) {
+        bool keep = true;
+        int p_eff = pos;
+        if (a.ring > 0) {
+            keep = pos >= a.seq_end[b] - a.ring;
+            p_eff = pos % a.ring;
+        }
+        if (keep) {
+            page = a.page_table[(size_t)b * a.table_stride + (p_eff >> 6)];
+            if (page < 0 && threadIdx.x == 0 && blockIdx.y == 0) atomicOr(a.status, MF_STATUS_BAD_POSITION);
+        }
+    }
+    pdl_wait();
+    const float* row = a.proj + (size_t)t * a.in_width;
+    const float* qs = row + a.q_off;
+    const float* ks = row + a.k_off;
+    float q_rinv = 1.0f, k_rinv = 1.0f;
+    if (a.q_norm_n > 0) {
+        float ss = 0.0f;
+        for (int i = threadIdx.x * 4; i < a.q_norm_n; i += blockDim.x * 4) {
+            const float4 x = *reinterpret_cast<const float4*>(qs + i);
+            ss = fmaf(x.x, x.x, ss); ss = fmaf(x.y, x.y, ss); ss = fmaf(x.z, x.z, ss); ss = fmaf(x.w, x.w, ss);
+        }
+        ss = block_sum(ss, scratch);
+        q_rinv = 1.0f / sqrtf(ss / (float)a.q_norm_n + a.eps);
+    }
+    if (a.k_norm_n > 0) {
+        float ss = 0.0f;
+        for (int i = threadIdx.x * 4; i < a.k_norm_n; i += blockDim.x * 4) {
+            const float4 x = *reinterpret_cast<const float4*>(ks + i);
+            ss = fmaf(x.x, x.x, ss); ss = fmaf(x.y, x.y, ss); ss = fmaf(x.z, x.z, ss); ss = fmaf(x.w, x.w, ss);
+        }
+        ss = block_sum(ss, scratch);
+        k_rinv = 1.0f / sqrtf(ss / (float)a.k_norm_n + a.eps);
+    }
+    __syncthreads();                                  // the cosines and sines are written
+    const int first = (blockIdx.y * blockDim.x + threadIdx.x) * 4, stride = gridDim.y * blockDim.x * 4;
+    T* q_out = (T*)a.q_out + (size_t)t * a.n_heads * a.qw;
+    const int nq = a.n_heads * a.qw;
+    for (int e = first; e < nq; e += stride) {
+        float y[4];
+        prep_group(qs, a.q_norm_w, a.q_norm_n, q_rinv, e % a.qw, e, a.q_rot_off, a, pr_cs, y);
+        PrepStore4<T>::store(q_out + e, y);
+    }
+    const int in_page = pos & (MF_PAGE - 1);
+    const int nk = a.n_kv * a.kw;
+    for (int e = first; e < nk; e += stride) {
+        const int hk = e / a.kw, d = e - hk * a.kw;
+        float y[4];
+        prep_group(ks, a.k_norm_w, a.k_norm_n, k_rinv, d, e, a.k_rot_off, a, pr_cs, y);
+        if (a.k_out) PrepStore4<T>::store((T*)a.k_out + (size_t)t * nk + e, y);
+        if (page >= 0)
+            PrepStore4<T>::store((T*)a.k_cache + (((size_t)page * a.n_kv + hk) * MF_PAGE + in_page) * a.kw + d, y);
+        if (a.v_from_k && d < a.vw) {
+            if (a.v_out) PrepStore4<T>::store((T*)a.v_out + ((size_t)t * a.n_kv + hk) * a.vw + d, y);
+            if (page >= 0 && a.v_cache)
+                PrepStore4<T>::store((T*)a.v_cache + (((size_t)page * a.n_kv + hk) * MF_PAGE + in_page) * a.vw + d, y);
+        }
+    }
+    if (!a.v_from_k) {
+        const float* vs = row + a.v_off;
+        const int nv = a.n_kv * a.vw;
+        for (int e = first; e < nv; e += stride) {
+            const int hk = e / a.vw, d = e - hk * a.vw;
+            const float4 x = *reinterpret_cast<const float4*>(vs + e);
+            const float y[4] = {x.x, x.y, x.z, x.w};
+            if (a.v_out) PrepStore4<T>::store((T*)a.v_out + (size_t)t * nv + e, y);
+            if (page >= 0)
+                PrepStore4<T>::store((T*)a.v_cache + (((size_t)page * a.n_kv + hk) * MF_PAGE + in_page) * a.vw + d, y);
+        }
+    }
+}
+
 extern "C" int mf_qk_prepare(const PrepArgs* args, int n_tokens, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     const PrepArgs a = *args;
@@ -172,7 +322,21 @@ extern "C" int mf_qk_prepare(const PrepArgs* args, int n_tokens, int dtype, cuda
         if (by < 1) by = 1;
     }
     dim3 grid(n_tokens, by);
-    if (dtype == MF_DTYPE_F32)
+    // the form with 16-byte accesses: every offset and width a multiple of 4 (8 for the half of a
+    // rotation in pairs (i, i + R/2)), every tensor on a 16-byte boundary
+    const int all = a.in_width | a.q_off | a.qw | a.q_norm_n | a.q_rot_off | a.k_off | a.kw | a.k_norm_n |
+                    a.k_rot_off | a.vw | (a.v_from_k ? 0 : a.v_off) | a.rot_dims |
+                    (a.rot_style == 0 ? a.rot_dims >> 1 : 0);
+    const uintptr_t ptrs = (uintptr_t)a.proj | (uintptr_t)a.q_norm_w | (uintptr_t)a.k_norm_w | (uintptr_t)a.q_out |
+                           (uintptr_t)a.k_out | (uintptr_t)a.v_out | (uintptr_t)a.k_cache | (uintptr_t)a.v_cache;
+    static int scalar = -1;             // MINFER_B200_QK_PREPARE=scalar: the element-by-element form always
+    if (scalar < 0) { const char* e = getenv("MINFER_B200_QK_PREPARE"); scalar = (e && e[0] == 's') ? 1 : 0; }
+    const bool vec = (all & 3) == 0 && (ptrs & 15) == 0 && !scalar;
+    if (vec && dtype == MF_DTYPE_F32)
+        mf_launch(qk_prepare_vec_kernel<float>, grid, dim3(256), smem, stream, a);
+    else if (vec && dtype == MF_DTYPE_BF16)
+        mf_launch(qk_prepare_vec_kernel<__nv_bfloat16>, grid, dim3(256), smem, stream, a);
+    else if (dtype == MF_DTYPE_F32)
         mf_launch(qk_prepare_kernel<float>, grid, dim3(256), smem, stream, a);
     else if (dtype == MF_DTYPE_BF16)
         mf_launch(qk_prepare_kernel<__nv_bfloat16>, grid, dim3(256), smem, stream, a);

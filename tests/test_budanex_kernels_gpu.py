@@ -138,24 +138,28 @@ def test_a_sink_that_outweighs_the_keys_and_a_cap_that_bites(dtype):
         assert err < _tol(dtype) * max(1.0, float(want.abs().max())), (cap, err)
 
 
+@pytest.mark.parametrize("sizes", [(3, 20, 1, 28, 18, 8, 12, 18, 18, 5),      # multiples of nothing
+                                   (3, 24, 2, 32, 20, 8, 16, 24, 40, 8),      # of 4: 16-byte accesses
+                                   (2, 64, 1, 128, 96, 32, 32, 96, 96, 0)])
 @pytest.mark.parametrize("style", ["half", "interleaved"])
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_prepare_kernel_norms_rotates_and_writes_pages(dtype, style):
+def test_prepare_kernel_norms_rotates_and_writes_pages(dtype, style, sizes):
     """Whole-segment norms with weights, a rotation of part of each head from an offset, values
     that are the key's first elements, and the cache pages, against plain functions."""
     from minfer_b200.kernels import api as K
     torch.manual_seed(11)
-    n, H, qw, G, kw, vw, rot, q_off_rot, k_off_rot = 70, 3, 20, 1, 28, 18, 8, 12, 18
-    width = H * qw + G * kw + 5
+    n = 70
+    H, qw, G, kw, vw, rot, q_off_rot, k_off_rot, k_norm_n, slack = sizes
+    width = H * qw + G * kw + slack
     proj = torch.randn(n, width, dtype=torch.float64)
     positions = list(range(1990, 1990 + n))            # large angles
     qn = 1 + 0.1 * torch.randn(H * qw, dtype=torch.float64)
-    kn = 1 + 0.1 * torch.randn(18, dtype=torch.float64)  # the first 18 elements of the key segment
+    kn = 1 + 0.1 * torch.randn(k_norm_n, dtype=torch.float64)  # the first elements of the key segment
     freqs = P.plain_frequencies(rot, 10000.0)
     mag = 1.25
     qs = P.rms_norm(proj[:, :H * qw], qn, 1e-5).view(n, H, qw).clone()
     ks = proj[:, H * qw:H * qw + G * kw].clone()
-    ks[:, :18] = P.rms_norm(ks[:, :18], kn, 1e-5)
+    ks[:, :k_norm_n] = P.rms_norm(ks[:, :k_norm_n], kn, 1e-5)
     ks = ks.view(n, G, kw)
     qs[:, :, q_off_rot:q_off_rot + rot] = P.rotate(qs[:, :, q_off_rot:q_off_rot + rot].contiguous(),
                                                    positions, freqs, style, mag)
